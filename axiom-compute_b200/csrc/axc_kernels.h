@@ -1,0 +1,45 @@
+// Internal launch interface between the C-ABI layer and the sm_100a kernels.
+#pragma once
+#include <cuda_runtime.h>
+#include <stddef.h>
+#include <stdint.h>
+
+namespace axc {
+
+// Tunables of the streaming matvec kernels.  0 = let the launcher choose.
+struct MatvecTuning {
+    int ctas_per_sm = 0;  // resident CTAs per SM the grid is sized for
+    int tile_rows = 0;    // rows per shared-memory stage
+    int stages = 0;       // stages in the ring
+    int threads = 0;      // threads per CTA (Q4_0 only; Q4_K derives it from the row length)
+    int evict_first = -1; // L2 evict-first hint on the weight stream (-1 = default)
+    int dry_run = 0;      // compute the launch geometry only, launch nothing
+};
+
+struct LaunchInfo {
+    int grid = 0, block = 0;
+    size_t smem = 0;
+    int tile_rows = 0, stages = 0, seg = 0, n_seg = 0;
+};
+
+// y[r] = dot(dequant(q row r), x) for r < rows; row r starts at q + r * n_sb * 144.
+// `status` is a device word that receives error bits (may be null).
+cudaError_t launch_q4k_matvec(const uint8_t* q, const float* x, float* y, uint32_t rows,
+                              uint32_t n_sb, uint32_t* status, cudaStream_t stream,
+                              const MatvecTuning& tune, int sm_count, LaunchInfo* info);
+// Same results as the reference's sequential fp32 loop, bit for bit (one thread per row).
+cudaError_t launch_q4k_matvec_seq(const uint8_t* q, const float* x, float* y, uint32_t rows,
+                                  uint32_t n_sb, cudaStream_t stream);
+// w[r][i] = bit-exact dequantised weight i of row r (x-index order).
+cudaError_t launch_q4k_dequant(const uint8_t* q, float* w, uint32_t rows, uint32_t n_sb,
+                               cudaStream_t stream);
+
+cudaError_t launch_q4_0_matvec(const uint8_t* q, const float* x, float* y, uint32_t rows,
+                               uint32_t n_blocks, uint32_t* status, cudaStream_t stream,
+                               const MatvecTuning& tune, int sm_count, LaunchInfo* info);
+cudaError_t launch_q4_0_matvec_seq(const uint8_t* q, const float* x, float* y, uint32_t rows,
+                                   uint32_t n_blocks, cudaStream_t stream);
+cudaError_t launch_q4_0_dequant(const uint8_t* q, float* w, uint32_t rows, uint32_t n_blocks,
+                                cudaStream_t stream);
+
+}  // namespace axc

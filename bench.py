@@ -1,0 +1,427 @@
+#!/usr/bin/env python
+"""Benchmark of the Q4_K_M dequant-matvec hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+Workload (N = 1): the Llama-3-8B up/gate shape, 14336 x 4096 Q4_K_M weights (16 superblocks of
+144 B per row), fp32 activations, batch 1, synthetic seeded data.  One *step* is one pass over
+a batch of 16 distinct weight matrices (16 matvec calls, 528 MB of weights, > 4x the 126 MB L2),
+so every call streams its weights from HBM.  The metric is effective bandwidth: algorithmic
+bytes (q + x + y = 33 103 872 B per call) / time.
+
+  value   weights, x and y resident in HBM; the step is replayed from a CUDA graph; CUDA events.
+  e2e     the same step through the reference-facing runtime call (``dispatch_handle`` over the
+          C ABI) with HOST buffers: per call x is copied host->device and y device->host inside
+          the timed region (weights resident via the empty-input rule); wall clock.
+  N > 1   one process per GPU; every rank holds its own 14336-row shard (global matrix
+          N x 14336 rows, weak scaling) and the y slices are assembled with an NCCL all-gather
+          after every call.  ``--scaling strong`` shards the fixed 14336 rows instead.
+
+``--impl reference`` times the reference's CPU implementation of the same path (the C
+restatement in oracle/, all host threads) on a bounded row sample of the same workload.
+"""
+from __future__ import annotations
+
+import argparse
+import importlib
+import json
+import os
+import statistics
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+ROWS, N_SB = 14336, 16                      # 14336 x 4096
+K_COLS = N_SB * 256
+N_MATRICES = 16
+Q_BYTES = ROWS * N_SB * 144
+ALGO_BYTES_PER_CALL = Q_BYTES + K_COLS * 4 + ROWS * 4   # 33 103 872
+METRIC = "q4k_matvec_14336x4096_effective_bandwidth"
+UNIT = "GB/s"
+FALLBACK_HBM_GBS = 6650.0
+
+
+def measured_peak():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        with open(p) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured (MEASURED_PEAKS.json hbm_gbs)"
+    except Exception:
+        return FALLBACK_HBM_GBS, "fallback (6.65 TB/s, earlier measurement on this pool)"
+
+
+# DRAM traffic of one q4k_matvec_stream_kernel launch from an ncu capture of this workload
+# (dram__bytes_read.sum + dram__bytes_write.sum); see profiles/.  None until captured.
+NCU_TRAFFIC_BYTES_PER_LAUNCH = None
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons through NVML while the timed region runs."""
+
+    def __init__(self, index: int):
+        self.samples, self.reasons, self.max_mhz, self.ok = [], set(), None, False
+        self._stop = threading.Event()
+        self._thr = None
+        try:
+            import pynvml
+            self.nv = pynvml
+            pynvml.nvmlInit()
+            self.h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = int(pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM))
+            self.ok = True
+        except Exception:
+            self.ok = False
+
+    def _run(self):
+        nv = self.nv
+        names = {
+            "hw_slowdown": getattr(nv, "nvmlClocksEventReasonHwSlowdown", 0x8),
+            "hw_thermal_slowdown": getattr(nv, "nvmlClocksEventReasonHwThermalSlowdown", 0x40),
+            "sw_thermal_slowdown": getattr(nv, "nvmlClocksEventReasonSwThermalSlowdown", 0x20),
+            "sw_power_cap": getattr(nv, "nvmlClocksEventReasonSwPowerCap", 0x4),
+            "hw_power_brake": getattr(nv, "nvmlClocksEventReasonHwPowerBrakeSlowdown", 0x80),
+        }
+        while not self._stop.is_set():
+            try:
+                self.samples.append(int(nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM)))
+                try:
+                    mask = int(nv.nvmlDeviceGetCurrentClocksEventReasons(self.h))
+                except Exception:
+                    mask = int(nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.h))
+                for k, bit in names.items():
+                    if mask & bit:
+                        self.reasons.add(k)
+            except Exception:
+                pass
+            time.sleep(0.01)
+
+    def start(self):
+        if self.ok:
+            self._thr = threading.Thread(target=self._run, daemon=True)
+            self._thr.start()
+
+    def stop(self):
+        if self._thr:
+            self._stop.set()
+            self._thr.join()
+
+    def summary(self):
+        if not self.ok or not self.samples:
+            return {"sm_mhz": None, "sm_max_mhz": self.max_mhz, "reasons": [], "samples": 0}
+        return {"sm_mhz": int(statistics.median(self.samples)), "sm_max_mhz": self.max_mhz,
+                "reasons": sorted(self.reasons), "samples": len(self.samples)}
+
+
+def host_cores() -> int:
+    try:
+        return len(os.sched_getaffinity(0))
+    except Exception:
+        return os.cpu_count() or 1
+
+
+def cpu_baseline_run(seconds_budget: float, threads: int, steps: int | None = None,
+                     warmup: int = 1):
+    """Times the CPU oracle (reference order, rows split over `threads`) on a row sample of the
+    benchmark matrix.  Returns (GB/s, sample description, ms per step, rows in the sample)."""
+    import oracle
+    synth = importlib.import_module("axiom-compute_b200.synth")
+    q = synth.q4k_weights(ROWS, N_SB, synth.config_seed(2, 0))
+    x = synth.activations(K_COLS, synth.config_seed(2, 1))
+    probe_rows = 1024
+    t0 = time.perf_counter()
+    oracle.matvec_rows("q4k", q, x, probe_rows, N_SB, threads=threads)
+    per_row = (time.perf_counter() - t0) / probe_rows
+    n_steps = steps if steps else 5
+    rows = int(seconds_budget / max(per_row * (n_steps + warmup), 1e-9))
+    rows = max(1024, min(ROWS, rows))
+    for _ in range(max(warmup, 1)):
+        oracle.matvec_rows("q4k", q, x, rows, N_SB, threads=threads)
+    times = []
+    for _ in range(n_steps):
+        t0 = time.perf_counter()
+        oracle.matvec_rows("q4k", q, x, rows, N_SB, threads=threads)
+        times.append(time.perf_counter() - t0)
+    bytes_step = rows * N_SB * 144 + K_COLS * 4 + rows * 4
+    best, mean = min(times), sum(times) / len(times)
+    sample = (f"{rows} of {ROWS} rows x {K_COLS} cols of the benchmark matrix per step, {n_steps} "
+              f"steps, reference operation order, {threads} thread(s); value from the mean step")
+    return bytes_step / mean / 1e9, sample, mean * 1e3, rows, bytes_step / best / 1e9
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    cores = host_cores()
+    budget = 90.0
+    gbs, sample, ms, rows, _best = cpu_baseline_run(budget, cores, steps=max(args.steps, 1),
+                                                    warmup=max(args.warmup, 1))
+    line = {
+        "impl": "reference", "metric": METRIC, "value": round(gbs, 4), "unit": UNIT,
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": round(ms, 4), "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": "q4k_matvec up/gate 14336x4096 (Llama-3-8B FFN), batch 1",
+                   "note": "reference CPU path (scalar fp32, reference operation order) on host cores"},
+        "cpu_baseline": {"value": round(gbs, 4), "unit": UNIT, "cores": cores, "kind": "port",
+                         "sample": sample},
+        "e2e": {"value": round(gbs, 4), "unit": UNIT, "h2d_bytes_per_step": 0,
+                "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def run_ours(args):
+    import torch
+    import torch.distributed as dist
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py: no CUDA device; this backend has no CPU path")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=dev)
+
+    pkg = importlib.import_module("axiom-compute_b200")
+    ops = importlib.import_module("axiom-compute_b200.ops")
+    synth = pkg.synth
+
+    strong = args.scaling == "strong" and world > 1
+    rows_local = ROWS // world if strong else ROWS
+    rows_global = ROWS if strong else ROWS * world
+
+    # ---- resident inputs: N_MATRICES distinct weight shards per rank ----
+    x_host = synth.activations(K_COLS, synth.config_seed(2, 1))
+    x_dev = torch.from_numpy(x_host).to(dev)
+    weights = []
+    base = synth.q4k_weights(ROWS, N_SB, synth.config_seed(2, 0) + 1000 * rank)
+    row_bytes = N_SB * 144
+    for m in range(N_MATRICES):
+        if m == 0:
+            w = base
+        else:
+            # distinct bytes per matrix without 16 full RNG passes: rotate rows and flip a byte lane
+            w = np.roll(base.reshape(ROWS, row_bytes), 97 * m, axis=0).copy()
+            w[:, 16 + (m % 128)] ^= np.uint8(m)
+            w = w.reshape(-1)
+        if strong:
+            w = w[rank * rows_local * row_bytes:(rank + 1) * rows_local * row_bytes]
+        weights.append(torch.from_numpy(np.ascontiguousarray(w)).to(dev))
+    y_local = [torch.empty(rows_local, dtype=torch.float32, device=dev) for _ in range(N_MATRICES)]
+    y_full = [torch.empty(rows_global, dtype=torch.float32, device=dev) for _ in range(N_MATRICES)] \
+        if world > 1 else None
+    status = ops.new_status(dev)
+
+    def step():
+        for m in range(N_MATRICES):
+            ops.q4k_matvec(weights[m], x_dev, rows_local, N_SB, y=y_local[m], status=status)
+            if world > 1:
+                dist.all_gather_into_tensor(y_full[m], y_local[m])
+
+    # ---- parity spot check against the oracle before timing (checker only) ----
+    step()
+    torch.cuda.synchronize()
+    if int(status.item()) != 0:
+        raise SystemExit(f"kernel status {int(status.item())}")
+    if rank == 0:
+        import oracle
+        rs = 64
+        y_ref = oracle.matvec_rows("q4k", weights[0][:rs * row_bytes].cpu().numpy(), x_host, rs, N_SB)
+        _y64, mag = oracle.matvec_rows_f64("q4k", weights[0][:rs * row_bytes].cpu().numpy(), x_host, rs, N_SB)
+        err = float((np.abs(y_local[0][:rs].cpu().numpy() - y_ref) / mag).max())
+        if not err <= 1e-5:
+            raise SystemExit(f"parity check failed before timing: norm-wise error {err:.3e}")
+
+    # ---- capture one step in a CUDA graph (launch overhead would otherwise dominate) ----
+    side = torch.cuda.Stream(device=dev)
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        for _ in range(2):
+            step()
+    torch.cuda.current_stream().wait_stream(side)
+    torch.cuda.synchronize()
+    graph = None
+    if not args.no_graph:
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            step()
+
+    def run_step():
+        if graph is not None:
+            graph.replay()
+        else:
+            step()
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(max(args.warmup, 3)):
+        run_step()
+    barrier()
+
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    ev0.record()
+    for _ in range(args.steps):
+        run_step()
+    ev1.record()
+    barrier()
+    elapsed_ms = ev0.elapsed_time(ev1)
+    # keep the GPU under the same load a little longer so the clock sampler sees it
+    t_end = time.perf_counter() + 0.4
+    while time.perf_counter() < t_end:
+        for _ in range(50):
+            run_step()
+        torch.cuda.synchronize()
+    sampler.stop()
+
+    t = torch.tensor([elapsed_ms], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    elapsed_ms = float(t.item())
+    calls = args.steps * N_MATRICES
+    bytes_per_call_local = rows_local * row_bytes + K_COLS * 4 + rows_local * 4
+    total_bytes = float(calls) * bytes_per_call_local * world
+    value = total_bytes / (elapsed_ms * 1e-3) / 1e9
+    us_per_call = elapsed_ms * 1e3 / calls
+
+    # ---- end to end through the runtime layer (host buffers, dispatch_handle) ----
+    e2e = None
+    if rank == 0 or world > 1:
+        e2e_val, h2d, d2h = run_e2e(pkg, local_rank, weights, x_host, rows_local, args, world,
+                                    dist if world > 1 else None, dev)
+        e2e = {"value": round(e2e_val, 3), "unit": UNIT, "h2d_bytes_per_step": h2d,
+               "d2h_bytes_per_step": d2h}
+
+    if world > 1:
+        dist.barrier()
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return
+
+    peak, peak_src = measured_peak()
+    achieved = bytes_per_call_local / (us_per_call * 1e-6) / 1e9   # per GPU
+    roofline = {"bound": "hbm", "achieved": round(achieved, 2), "peak": peak, "unit": "GB/s",
+                "frac": round(achieved / peak, 4), "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH,
+                "kernel": "q4k_matvec_stream_kernel", "algorithmic_bytes_per_launch": bytes_per_call_local,
+                "peak_source": peak_src,
+                "note": "achieved = algorithmic bytes per launch / mean launch-to-launch time over "
+                        "the timed region (includes inter-kernel gaps"
+                        + (" and the all-gather" if world > 1 else "") + ")"}
+
+    cores = host_cores()
+    cpu = None
+    if world == 1 and not args.skip_cpu:
+        gbs, sample, _ms, _rows, _best = cpu_baseline_run(12.0, cores)
+        gbs1, _s1, _m1, _r1, _b1 = cpu_baseline_run(6.0, 1)
+        cpu = {"value": round(gbs, 4), "unit": UNIT, "cores": cores, "kind": "port",
+               "sample": sample, "single_thread_value": round(gbs1, 4)}
+
+    line = {
+        "metric": METRIC, "value": round(value, 2), "unit": UNIT, "n_gpus": world,
+        "steps": args.steps, "warmup": max(args.warmup, 3),
+        "ms_per_step": round(elapsed_ms / args.steps, 6), "higher_is_better": True,
+        "scaling": "strong" if strong else "weak", "vs_baseline": None, "dtype": "f32",
+        "data": "synthetic",
+        "config": {
+            "workload": "q4k_matvec up/gate 14336x4096 (Llama-3-8B FFN), batch 1",
+            "rows_per_gpu": rows_local, "global_rows": rows_global, "cols": K_COLS,
+            "calls_per_step": N_MATRICES,
+            "l2": f"inputs larger than L2: {N_MATRICES} distinct weight matrices per GPU "
+                  f"({N_MATRICES * rows_local * row_bytes / 1e6:.0f} MB) visited round-robin",
+            "launch": "cuda_graph" if graph is not None else "stream",
+            "parallelism": "single GPU" if world == 1 else
+                           f"rows sharded over {world} GPUs + NCCL all-gather of y per call",
+        },
+        "us_per_call": round(us_per_call, 4),
+        "pct_of_8TBs": round(100.0 * (bytes_per_call_local / (us_per_call * 1e-6)) / 8e12, 2),
+        "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e,
+        "gpu_launches": calls, "clocks": sampler.summary(),
+    }
+    print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def run_e2e(pkg, device_index, weights, x_host, rows_local, args, world, dist, dev):
+    """Same step through CudaContext.dispatch_handle with host buffers (wall clock)."""
+    import struct
+    import torch
+    ctx = pkg.CudaContext.new_with_options(pkg.CudaContextOptions(None, device_index, None))
+    plan = pkg.q4_matvec_binding_plan("q4km_dequant_matvec")
+    handles = []
+    pc = struct.pack("<I", N_SB)
+    for m in range(N_MATRICES):
+        h = ctx.prepare_kernel([0x07230203, m], plan, 4, "q4km_dequant_matvec", spirv_hash=0xE2E0 + m)
+        # upload this matrix once (not timed): the empty-input rule keeps it resident afterwards
+        ctx.dispatch_handle(h, (rows_local, 1, 1), [weights[m].cpu().numpy(), x_host, b""],
+                            [0, 0, rows_local * 4], pc)
+        handles.append(h)
+    x_bytes = x_host.tobytes()
+    y_full = torch.empty(rows_local * world, dtype=torch.float32, device=dev) if world > 1 else None
+
+    def step():
+        for m in range(N_MATRICES):
+            out = ctx.dispatch_handle(handles[m], (rows_local, 1, 1), [b"", x_bytes, b""],
+                                      [0, 0, rows_local * 4], pc)
+            if world > 1:
+                y_loc = torch.frombuffer(out[2], dtype=torch.float32).to(dev, non_blocking=True)
+                dist.all_gather_into_tensor(y_full, y_loc)
+        return out
+
+    steps = max(1, min(args.steps, 200))
+    for _ in range(3):
+        step()
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        step()
+    torch.cuda.synchronize()
+    dt = time.perf_counter() - t0
+    t = torch.tensor([dt], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    dt = float(t.item())
+    bytes_per_call = rows_local * N_SB * 144 + K_COLS * 4 + rows_local * 4
+    val = steps * N_MATRICES * bytes_per_call * world / dt / 1e9
+    for h in handles:
+        h.drop()
+    ctx.drop()
+    return val, N_MATRICES * K_COLS * 4, N_MATRICES * rows_local * 4
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=2000)
+    ap.add_argument("--warmup", type=int, default=20)
+    ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
+    ap.add_argument("--scaling", choices=["weak", "strong"], default="weak")
+    ap.add_argument("--no-graph", action="store_true", help="launch from the stream, no CUDA graph")
+    ap.add_argument("--skip-cpu", action="store_true", help="skip the CPU baseline leg")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,233 @@
+/*
+ * axc_cuda.h -- C ABI of libaxc_cuda.so, the B200 (sm_100a) backend for AXIOM-Compute's
+ * quantised dequant-matvec path.
+ *
+ * Two layers:
+ *   1. A runtime layer that mirrors axc-runtime's context / kernel-handle / dispatch API one
+ *      to one (host buffers in, host buffers out, typed error codes), so a Rust `cuda`
+ *      backend module can implement VulkanContext's method set by calling it.
+ *   2. A device layer that launches the kernels on caller-owned device memory and a caller's
+ *      stream, for callers that keep weights and activations resident (decode loops,
+ *      multi-GPU drivers, benchmarks).
+ *
+ * Conventions: every function returning `int` returns an axc_status (0 = AXC_OK).  No C++
+ * exception crosses this boundary.  After a non-zero status, axc_cuda_last_error_detail()
+ * gives a thread-local, human-readable detail string and axc_cuda_last_error_fields() the
+ * typed fields of the matching DispatchError variant.  All functions are thread-safe;
+ * dispatches on one kernel handle serialise on a per-handle mutex, different handles may run
+ * concurrently (crates/axc-runtime/src/context.rs:494-497).
+ *
+ * Paths cited below are relative to the AXIOM-Compute repository.
+ */
+#ifndef AXC_CUDA_H
+#define AXC_CUDA_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* One code per DispatchError variant that this backend can raise
+ * (crates/axc-runtime/src/error.rs:27-195), plus AXC_ERR_INVALID_ARGUMENT for a null or
+ * malformed argument at the C boundary itself (unrepresentable in the Rust API). */
+typedef enum axc_status {
+    AXC_OK = 0,
+    AXC_ERR_NO_SUPPORTED_DEVICE = 3,              /* NoSupportedDevice */
+    AXC_ERR_DEVICE_CREATION_FAILED = 5,           /* DeviceCreationFailed(String) */
+    AXC_ERR_PIPELINE_CREATION_FAILED = 10,        /* PipelineCreationFailed(String) */
+    AXC_ERR_BUFFER_ALLOCATION_FAILED = 11,        /* BufferAllocationFailed{binding,size,reason} */
+    AXC_ERR_QUEUE_SUBMIT_FAILED = 15,             /* QueueSubmitFailed(String) */
+    AXC_ERR_FENCE_TIMEOUT = 16,                   /* FenceTimeout{timeout_ns} */
+    AXC_ERR_READBACK_FAILED = 17,                 /* ReadbackFailed{binding,reason} */
+    AXC_ERR_BINDING_COUNT_MISMATCH = 18,          /* BindingCountMismatch{expected,provided} */
+    AXC_ERR_PUSH_CONSTANT_SIZE_MISMATCH = 19,     /* PushConstantSizeMismatch{expected,provided} */
+    AXC_ERR_WORKGROUP_COUNT_EXCEEDS_LIMIT = 20,   /* WorkgroupCountExceedsDeviceLimit{requested,max} */
+    AXC_ERR_STAGING_COPY_FAILED = 25,             /* StagingCopyFailed{binding,direction,reason} */
+    AXC_ERR_INVALID_ARGUMENT = 100
+} axc_status;
+
+/* CopyDirection (crates/axc-runtime/src/error.rs:14-20). */
+enum { AXC_COPY_HOST_TO_DEVICE = 0, AXC_COPY_DEVICE_TO_HOST = 1 };
+
+/* Typed payload of the last error on this thread (fields unused by a variant are zero). */
+typedef struct axc_error_fields {
+    uint32_t binding;
+    uint32_t direction;      /* AXC_COPY_* */
+    uint64_t size;
+    uint64_t expected;
+    uint64_t provided;
+    uint64_t timeout_ns;
+    uint32_t requested[3];
+    uint32_t max[3];
+} axc_error_fields;
+
+typedef struct axc_ctx axc_ctx;       /* <-> VulkanContext  (context.rs:160-373) */
+typedef struct axc_kernel axc_kernel; /* <-> KernelHandle   (kernel_handle.rs:44-151) */
+
+/* <-> VulkanContextOptions (context.rs:76-109). */
+typedef struct axc_ctx_opts {
+    int32_t physical_device_index; /* CUDA ordinal; -1 = AXC_PHYSICAL_DEVICE_INDEX or 0 */
+    uint64_t fence_timeout_ms;     /* 0 = AXC_FENCE_TIMEOUT_MS, read per dispatch, else 10 000 */
+    const char* pipeline_cache_path; /* accepted and ignored: kernels are compiled ahead of time */
+} axc_ctx_opts;
+
+/* Element type / access of one buffer binding (axc-hir ScalarTy / BufferAccess,
+ * crates/axc-hir/src/ty.rs:13-26, crates/axc-hir/src/buffer.rs:16-49). */
+enum { AXC_TY_U8 = 1, AXC_TY_F32 = 2, AXC_TY_U32 = 3, AXC_TY_OTHER = 0 };
+enum { AXC_ACCESS_READ_ONLY = 1, AXC_ACCESS_READ_WRITE = 2, AXC_ACCESS_WRITE_ONLY = 3 };
+
+/* One BufferBindingSlot of the ParamBindingPlan (crates/axc-hir/src/param.rs:66-78). */
+typedef struct axc_buf_desc {
+    uint32_t elem_ty;          /* AXC_TY_* */
+    uint32_t access;           /* AXC_ACCESS_* */
+    uint32_t buffer_position;  /* = descriptor binding index */
+    uint32_t position;         /* position in the kernel's parameter list */
+} axc_buf_desc;
+
+/* Device-side timing of one dispatch (CUDA events on the context's stream). */
+typedef struct axc_dispatch_stats {
+    uint64_t h2d_ns;
+    uint64_t kernel_ns;
+    uint64_t d2h_ns;
+    uint64_t total_device_ns;
+    uint32_t rows_effective;   /* rows actually computed after clamping to the buffer sizes */
+    uint32_t blocks_per_row;   /* push constant n_superblocks / n_blocks */
+} axc_dispatch_stats;
+
+/* ---- availability (crates/axc-runtime/src/icd.rs:22-80) ---- */
+
+/* <-> probe_vulkan_available(): 1 if at least one compute-capability-10.x device exists. */
+int axc_cuda_probe(void);
+/* <-> gpu_tests_enabled(): 1 iff AXC_ENABLE_GPU_TESTS == "1". */
+int axc_cuda_gpu_tests_enabled(void);
+/* Number of CUDA devices (0 when the driver is absent). */
+int axc_cuda_device_count(void);
+
+/* ---- context (context.rs:160-373, 569-625) ---- */
+
+/* <-> VulkanContext::new_with_options; opts == NULL <-> VulkanContext::new() (from_env). */
+int axc_cuda_ctx_create(const axc_ctx_opts* opts, axc_ctx** out);
+/* <-> Drop for VulkanContext: waits for the device to go idle, then releases.  Kernel
+ * handles stay valid afterwards (kernel_handle_outlives_context, AT-827). */
+void axc_cuda_ctx_destroy(axc_ctx* ctx);
+/* <-> physical_device_name(): NUL-terminated copy into buf; returns the full length. */
+size_t axc_cuda_ctx_device_name(const axc_ctx* ctx, char* buf, size_t cap);
+/* <-> max_compute_work_group_count(). */
+void axc_cuda_ctx_max_grid(const axc_ctx* ctx, uint32_t out[3]);
+int axc_cuda_ctx_device_index(const axc_ctx* ctx);
+int axc_cuda_ctx_sm_count(const axc_ctx* ctx);
+
+/* ---- kernel handles (context.rs:392-486, kernel_handle.rs:44-151,216-246) ---- */
+
+/* <-> prepare_kernel(spirv, plan, pc_total, entry_point).  The SPIR-V is not consumed; its
+ * xxh3 hash and the plan's hash form the cache key with pc_total_bytes, exactly as in
+ * make_cache_key.  Two calls with the same key while the first handle is alive return the
+ * same object with one more reference.  entry_point selects the kernel:
+ * "q4km_dequant_matvec" or "q4_0_dequant_matvec" with buffers [U8 RO, F32 RO, F32 RW] and a
+ * 4-byte push-constant block; anything else is AXC_ERR_PIPELINE_CREATION_FAILED. */
+int axc_cuda_prepare_kernel(axc_ctx* ctx, const char* entry_point, const axc_buf_desc* bufs,
+                            uint32_t n_bufs, uint32_t pc_total_bytes, uint64_t spirv_hash,
+                            uint64_t plan_hash, axc_kernel** out);
+void axc_cuda_kernel_retain(axc_kernel* k);   /* <-> KernelHandle::clone */
+void axc_cuda_kernel_release(axc_kernel* k);  /* <-> Drop for KernelHandle */
+/* <-> KernelHandle::buffer_sizes(): device size of each allocated binding slot; returns the
+ * number of slots (may exceed cap; only cap entries are written). */
+uint32_t axc_cuda_kernel_buffer_sizes(const axc_kernel* k, uint64_t* out, uint32_t cap);
+/* <-> KernelHandle::cache_key(): (spirv_hash, plan_hash, pc bytes). */
+void axc_cuda_kernel_cache_key(const axc_kernel* k, uint64_t* spirv_hash, uint64_t* plan_hash,
+                               uint32_t* pc_total_bytes);
+/* Strict mode: when non-zero the handle runs the reference-order kernel whose y is
+ * bit-identical to the CPU reference (one thread per row; slow).  Default 0. */
+void axc_cuda_kernel_set_strict_order(axc_kernel* k, int strict);
+
+/* ---- dispatch (context.rs:498-547, kernel_handle.rs:295-393,410-738, dispatch.rs:56-132) ----
+ *
+ * <-> dispatch_handle(handle, workgroups, inputs, output_sizes, push_constants).
+ *   inputs[i] / input_lens[i]: host bytes for binding i; length 0 skips the upload and the
+ *     device buffer keeps its contents (resident weights).
+ *   outputs[i] / output_sizes[i]: caller-allocated host buffers; size 0 skips the readback
+ *     (outputs[i] may then be NULL).  The Rust side wraps them into Vec<Vec<u8>>.
+ *   Validation order, before any allocation: n_inputs, n_outputs, pc_len, workgroup limits.
+ *   Device buffers grow to round_up_pow2(max(in, out, 4)) and never shrink.
+ *   Rows come from the grid: rows = workgroups[0]; the push constant keeps its reference
+ *   meaning (n_superblocks / n_blocks PER ROW).  rows is clamped to what the q and y buffers
+ *   hold; workgroups = [1,1,1] is exactly the reference's single-output behaviour, and
+ *   n = 0 writes y[0] = +0.0.
+ *   The wait for completion is bounded by the fence timeout -> AXC_ERR_FENCE_TIMEOUT.
+ */
+int axc_cuda_dispatch(axc_ctx* ctx, axc_kernel* k, const uint32_t workgroups[3],
+                      const void* const* inputs, const size_t* input_lens, uint32_t n_inputs,
+                      void* const* outputs, const size_t* output_sizes, uint32_t n_outputs,
+                      const void* push_constants, size_t pc_len, axc_dispatch_stats* stats);
+
+/* <-> VulkanContext::dispatch(DispatchRequest) (dispatch.rs:109-132): validate, prepare,
+ * dispatch once, release. */
+int axc_cuda_dispatch_oneshot(axc_ctx* ctx, const char* entry_point, const axc_buf_desc* bufs,
+                              uint32_t n_bufs, uint32_t pc_total_bytes, uint64_t spirv_hash,
+                              uint64_t plan_hash, const uint32_t workgroups[3],
+                              const void* const* inputs, const size_t* input_lens,
+                              uint32_t n_inputs, void* const* outputs, const size_t* output_sizes,
+                              uint32_t n_outputs, const void* push_constants, size_t pc_len,
+                              axc_dispatch_stats* stats);
+
+/* <-> the timing loop of bench_variant (crates/axc-driver/src/mcp/tools/bench_variant.rs:
+ * 284-301): sample_count wall-clock timed dispatch_handle calls; samples_ns receives each
+ * sample, *median_ns = sorted[len/2].  device_kernel_ns (nullable) receives the per-sample
+ * device time of the kernel alone. */
+int axc_cuda_bench_dispatch(axc_ctx* ctx, axc_kernel* k, const uint32_t workgroups[3],
+                            const void* const* inputs, const size_t* input_lens, uint32_t n_inputs,
+                            void* const* outputs, const size_t* output_sizes, uint32_t n_outputs,
+                            const void* push_constants, size_t pc_len, uint32_t sample_count,
+                            uint64_t* samples_ns, uint64_t* median_ns, uint64_t* device_kernel_ns);
+
+/* ---- errors (error.rs) ---- */
+const char* axc_cuda_strerror(int status);
+size_t axc_cuda_last_error_detail(char* buf, size_t cap);
+void axc_cuda_last_error_fields(axc_error_fields* out);
+
+/* ---- device layer: kernels on caller-owned device memory ----
+ *
+ * q, x, y are device pointers (16-byte aligned), stream is a cudaStream_t (NULL = default
+ * stream), status is an optional device uint32 that receives kernel error bits.  These are
+ * the same kernels axc_cuda_dispatch launches for examples/q4km_dequant_matvec.axc and
+ * examples/q4_0_dequant_matvec.axc, generalised from one row to `rows` rows.
+ */
+typedef struct axc_tuning {
+    int32_t ctas_per_sm; /* 0 = default */
+    int32_t tile_rows;
+    int32_t stages;
+    int32_t threads;
+    int32_t evict_first; /* -1 = default */
+} axc_tuning;
+
+int axc_cuda_q4k_matvec(const void* q, const float* x, float* y, uint32_t rows,
+                        uint32_t n_superblocks, void* stream, uint32_t* status,
+                        const axc_tuning* tuning);
+int axc_cuda_q4_0_matvec(const void* q, const float* x, float* y, uint32_t rows,
+                         uint32_t n_blocks, void* stream, uint32_t* status,
+                         const axc_tuning* tuning);
+/* Reference-order variants: y bit-identical to q4km_dequant_matvec_cpu /
+ * q4_0_dequant_matvec_cpu (common_helpers.rs:411-461, benches/common.rs:212-259). */
+int axc_cuda_q4k_matvec_seq(const void* q, const float* x, float* y, uint32_t rows,
+                            uint32_t n_superblocks, void* stream);
+int axc_cuda_q4_0_matvec_seq(const void* q, const float* x, float* y, uint32_t rows,
+                             uint32_t n_blocks, void* stream);
+/* Dequantised weights, bit-identical to the reference's per-element values, shape
+ * [rows][n * 256] (Q4_K_M) or [rows][n * 32] (Q4_0) in x-index order. */
+int axc_cuda_q4k_dequant(const void* q, float* w, uint32_t rows, uint32_t n_superblocks,
+                         void* stream);
+int axc_cuda_q4_0_dequant(const void* q, float* w, uint32_t rows, uint32_t n_blocks,
+                          void* stream);
+/* Launch geometry the matvec launchers would use (no launch). */
+int axc_cuda_q4k_matvec_plan(uint32_t rows, uint32_t n_superblocks, const axc_tuning* tuning,
+                             int32_t sm_count, int32_t out_grid_block_smem_tile_stages[5]);
+
+/* Library version: major * 10000 + minor * 100 + patch. */
+int axc_cuda_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* AXC_CUDA_H */

@@ -1,0 +1,301 @@
+"""Parity of the CUDA kernels with the CPU oracle, through the C ABI (device layer).
+
+Bars: dequantised weights bit-exact; reference-order kernels bit-exact in y; the fast kernels
+within 1e-5 of the oracle per row, measured norm-wise (|dy| / sum_i |w_i x_i|), because the
+reference's own sequential fp32 sum misses the exact dot product by more than 1e-5 of |y| on a
+few percent of rows (cancellation), so no reordered sum can meet a strict |dy|/|y| bound on
+every row.  The strict figure is still computed and bounded in distribution.
+"""
+import hashlib
+
+import numpy as np
+import pytest
+
+import oracle
+
+torch = pytest.importorskip("torch")
+pytestmark = pytest.mark.gpu
+
+NORMWISE_TOL = 1e-5     # the stated output tolerance
+REFERENCE_TOL = 1e-3    # the reference's own GPU-vs-CPU tolerance (compile_q4km_dequant_matvec.rs:946-956)
+
+
+def dev(a):
+    return torch.from_numpy(np.ascontiguousarray(a)).cuda()
+
+
+def rel_err_reference_rule(gpu, cpu):
+    """|gpu - cpu| / |cpu| when |cpu| > 1e-10, else absolute (the reference's rule)."""
+    gpu, cpu = np.asarray(gpu, np.float64), np.asarray(cpu, np.float64)
+    d = np.abs(gpu - cpu)
+    return np.where(np.abs(cpu) > 1e-10, d / np.maximum(np.abs(cpu), 1e-300), d)
+
+
+def check_fast(fmt, y_gpu, q, x, rows, n):
+    y_ref = oracle.matvec_rows(fmt, q, x, rows, n)
+    y64, mag = oracle.matvec_rows_f64(fmt, q, x, rows, n)
+    y_gpu = np.asarray(y_gpu, np.float64)
+    mag = np.maximum(mag, 1e-300)
+    normwise = np.abs(y_gpu - y_ref) / mag
+    assert normwise.max() <= NORMWISE_TOL, f"norm-wise error {normwise.max():.3e}"
+    # against exact arithmetic the GPU must be at least as good as the fp32-sequential reference
+    e_gpu = np.abs(y_gpu - y64) / mag
+    e_ref = np.abs(y_ref - y64) / mag
+    assert e_gpu.max() <= max(2.0 * e_ref.max(), 5e-7), (e_gpu.max(), e_ref.max())
+    strict = rel_err_reference_rule(y_gpu, y_ref)
+    assert strict.max() < REFERENCE_TOL or rows > 1000, strict.max()
+    return strict
+
+
+# ---------------------------------------------------------------------------------- Q4_K_M
+
+@pytest.mark.parametrize("rows,n_sb", [(1, 1), (3, 2), (8, 16), (9, 3), (7, 56), (2, 128), (5, 200)])
+def test_q4k_dequant_is_bit_exact(ops, synth, rows, n_sb):
+    q = synth.q4k_weights(rows, n_sb, 100 + rows * 7 + n_sb)
+    w = ops.q4k_dequant(dev(q), rows, n_sb).cpu().numpy()
+    w_ref = oracle.dequant_rows("q4k", q, rows, n_sb)
+    assert (w.view(np.uint32) == w_ref.view(np.uint32)).all()
+
+
+def test_q4k_dequant_lcg_fixture_matches_golden_hash(ops, golden):
+    for fx in golden["lcg"]["fixtures"]:
+        q, _x = oracle.generate_q4km_test_data(fx["n_superblocks"], fx["seed"])
+        w = ops.q4k_dequant(dev(q), 1, fx["n_superblocks"]).cpu().numpy()
+        assert hashlib.sha256(w.tobytes()).hexdigest() == fx["w_sha256"]
+
+
+def test_q4k_dequant_special_scales_bit_exact(ops, synth):
+    """fp16 subnormals, zeros, Inf and NaN in d / dmin are widened exactly and propagate."""
+    rows, n_sb = 4, 8
+    q = synth.q4k_weights(rows, n_sb, 9).reshape(-1, 144)
+    specials = [0x0001, 0x03FF, 0x0000, 0x8000, 0x7C00, 0xFC00, 0x7E00, 0x0400, 0x7BFF]
+    for i in range(q.shape[0]):
+        q[i, 0:2] = np.frombuffer(np.uint16(specials[i % len(specials)]).tobytes(), np.uint8)
+        q[i, 2:4] = np.frombuffer(np.uint16(specials[(i * 5 + 3) % len(specials)]).tobytes(), np.uint8)
+    q = q.reshape(-1)
+    w = ops.q4k_dequant(dev(q), rows, n_sb).cpu().numpy().view(np.uint32)
+    w_ref = oracle.dequant_rows("q4k", q, rows, n_sb).view(np.uint32)
+    nan = (w_ref & 0x7FFFFFFF) > 0x7F800000
+    assert ((w == w_ref) | nan).all()
+    assert (((w & 0x7FFFFFFF) > 0x7F800000) == nan).all()
+
+
+def test_q4k_seq_kernel_is_bit_identical_on_the_reference_fixture(ops, golden):
+    """The reference's own parity case (AT-1324 / AT-1331: n = 128, seed 0xDEADBEEF, one output)
+    and its bench pre-flight seed, in reference operation order: same bits as the CPU function."""
+    for fx in golden["lcg"]["fixtures"]:
+        n = fx["n_superblocks"]
+        q, x = oracle.generate_q4km_test_data(n, fx["seed"])
+        y = ops.q4k_matvec_seq(dev(q), dev(x), 1, n).cpu().numpy()
+        assert int(y.view(np.uint32)[0]) == fx["y_bits"]
+
+
+@pytest.mark.parametrize("rows,n_sb", [(8, 16), (33, 5), (4, 56)])
+def test_q4k_seq_kernel_bit_identical_rows(ops, synth, rows, n_sb):
+    q = synth.q4k_weights(rows, n_sb, 31 + rows)
+    x = synth.activations(n_sb * 256, 32 + rows)
+    y = ops.q4k_matvec_seq(dev(q), dev(x), rows, n_sb).cpu().numpy()
+    y_ref = oracle.matvec_rows("q4k", q, x, rows, n_sb)
+    assert (y.view(np.uint32) == y_ref.view(np.uint32)).all()
+
+
+def test_q4k_fast_kernel_on_the_reference_fixture(ops, golden):
+    for fx in golden["lcg"]["fixtures"]:
+        n = fx["n_superblocks"]
+        q, x = oracle.generate_q4km_test_data(n, fx["seed"])
+        st = ops.new_status()
+        y = ops.q4k_matvec(dev(q), dev(x), 1, n, status=st).cpu().numpy()
+        assert int(st.item()) == 0
+        cpu = np.array([fx["y_bits"]], np.uint32).view(np.float32)
+        assert rel_err_reference_rule(y, cpu)[0] < 1e-5
+        check_fast("q4k", y, q, x, 1, n)
+
+
+@pytest.mark.parametrize("rows,n_sb", [
+    (8, 16),        # config 0: 8 rows x 4096
+    (1, 1), (1, 2), (2, 3), (7, 16), (9, 16), (1, 16), (300, 16), (1000, 16),
+    (5, 56), (64, 56),          # down-projection row length (K = 14336)
+    (6, 32), (3, 112),          # 70B-shaped rows (K = 8192, 28672)
+    (2, 128), (3, 129), (2, 200), (1, 512),   # K segmented beyond 128 superblocks
+])
+def test_q4k_fast_kernel_matches_oracle(ops, synth, rows, n_sb):
+    q = synth.q4k_weights(rows, n_sb, 1000 + rows * 13 + n_sb)
+    x = synth.activations(n_sb * 256, 2000 + rows + n_sb)
+    st = ops.new_status()
+    y = ops.q4k_matvec(dev(q), dev(x), rows, n_sb, status=st).cpu().numpy()
+    assert int(st.item()) == 0
+    check_fast("q4k", y, q, x, rows, n_sb)
+
+
+@pytest.mark.parametrize("scale_exp", [-100, -60, -20, 20, 60, 100])
+def test_q4k_fast_kernel_is_scale_invariant(ops, synth, scale_exp):
+    """Activations of any magnitude: the power-of-two pre-scaling must not lose them."""
+    rows, n_sb = 16, 16
+    q = synth.q4k_weights(rows, n_sb, 77)
+    x = (synth.activations(n_sb * 256, 78).astype(np.float64) * 2.0 ** scale_exp).astype(np.float32)
+    y = ops.q4k_matvec(dev(q), dev(x), rows, n_sb).cpu().numpy()
+    check_fast("q4k", y, q, x, rows, n_sb)
+
+
+def test_q4k_fast_kernel_mixed_magnitudes_and_zeros(ops, synth):
+    rows, n_sb = 12, 16
+    q = synth.q4k_weights(rows, n_sb, 79)
+    x = synth.activations(n_sb * 256, 80)
+    x[:64] = 0.0                      # a whole chunk of zeros
+    x[64:128] *= 1e-30                # a tiny chunk
+    x[128:192] *= 1e20                # a huge chunk
+    x[300] = 0.0
+    y = ops.q4k_matvec(dev(q), dev(x), rows, n_sb).cpu().numpy()
+    check_fast("q4k", y, q, x, rows, n_sb)
+
+
+def test_q4k_nonfinite_inputs_propagate_without_trapping(ops, synth):
+    """bench_variant feeds uniform random bytes: fp16 scales and fp32 activations may be Inf/NaN.
+    Rows the oracle makes non-finite must come out non-finite; finite rows must still match."""
+    rows, n_sb = 32, 4
+    rng = np.random.default_rng(5)
+    q = rng.integers(0, 256, rows * n_sb * 144, dtype=np.uint8)
+    x = synth.activations(n_sb * 256, 6)
+    st = ops.new_status()
+    y = ops.q4k_matvec(dev(q), dev(x), rows, n_sb, status=st).cpu().numpy()
+    assert int(st.item()) == 0
+    with np.errstate(all="ignore"):
+        y_ref = oracle.matvec_rows("q4k", q, x, rows, n_sb)
+    finite = np.isfinite(y_ref)
+    assert (np.isfinite(y) == finite).all()
+    x2 = x.copy()
+    x2[5] = np.inf
+    x2[700] = np.nan
+    y2 = ops.q4k_matvec(dev(synth.q4k_weights(rows, n_sb, 8)), dev(x2), rows, n_sb).cpu().numpy()
+    assert not np.isfinite(y2).any()
+
+
+def test_q4k_zero_superblocks_writes_positive_zero(ops):
+    q = torch.zeros(16, dtype=torch.uint8, device="cuda")
+    x = torch.zeros(4, dtype=torch.float32, device="cuda")
+    y = torch.full((5,), 7.0, dtype=torch.float32, device="cuda")
+    ops.q4k_matvec(q, x, 5, 0, y=y)
+    assert (y.cpu().numpy().view(np.uint32) == 0).all()
+
+
+def test_q4k_tuning_variants_agree(ops, synth):
+    rows, n_sb = 513, 16
+    q = synth.q4k_weights(rows, n_sb, 91)
+    x = synth.activations(n_sb * 256, 92)
+    y_ref = oracle.matvec_rows("q4k", q, x, rows, n_sb)
+    _y64, mag = oracle.matvec_rows_f64("q4k", q, x, rows, n_sb)
+    for kw in (dict(ctas_per_sm=1), dict(ctas_per_sm=2, tile_rows=4, stages=2), dict(tile_rows=16),
+               dict(stages=1), dict(evict_first=1), dict(ctas_per_sm=1, tile_rows=32, stages=3)):
+        y = ops.q4k_matvec(dev(q), dev(x), rows, n_sb, tuning=ops.make_tuning(**kw)).cpu().numpy()
+        assert (np.abs(y - y_ref) / mag).max() <= NORMWISE_TOL, kw
+
+
+# ---------------------------------------------------------------------------------- Q4_0
+
+@pytest.mark.parametrize("rows,n", [(1, 1), (3, 2), (5, 7), (8, 128), (2, 1024), (2, 1030)])
+def test_q4_0_dequant_is_bit_exact(ops, synth, rows, n):
+    q = synth.q4_0_weights(rows, n, 300 + rows + n)
+    w = ops.q4_0_dequant(dev(q), rows, n).cpu().numpy()
+    w_ref = oracle.dequant_rows("q4_0", q, rows, n)
+    assert (w.view(np.uint32) == w_ref.view(np.uint32)).all()
+
+
+def test_q4_0_reference_layout_fixtures_on_gpu(ops, golden):
+    for case in golden["known"]["q4_0_layout"]:
+        q = np.zeros(32, np.uint8)
+        q[:18] = case["q"]
+        x = np.array(case["x"], np.float32)
+        for fn in (ops.q4_0_matvec, ops.q4_0_matvec_seq):
+            y = fn(dev(q), dev(x), 1, 1).cpu().numpy()
+            assert abs(float(y[0]) - case["expected"]) < case["abs_tol"]
+
+
+@pytest.mark.parametrize("rows,n", [(1, 128), (1, 1024), (17, 5), (40, 128)])
+def test_q4_0_seq_kernel_is_bit_identical(ops, synth, rows, n):
+    q = synth.q4_0_weights(rows, n, 400 + rows + n)
+    x = np.random.default_rng(n).uniform(-1, 1, n * 32).astype(np.float32)
+    y = ops.q4_0_matvec_seq(dev(q), dev(x), rows, n).cpu().numpy()
+    y_ref = oracle.matvec_rows("q4_0", q, x, rows, n)
+    assert (y.view(np.uint32) == y_ref.view(np.uint32)).all()
+
+
+@pytest.mark.parametrize("rows,n", [
+    (1, 128), (1, 1024),            # the reference's bench sizes (one output)
+    (1, 1), (1, 2), (3, 3), (5, 7), (9, 2), (7, 10), (33, 64), (100, 128), (513, 128),
+    (3, 66), (2, 448), (4, 1024), (2, 1026), (3, 2049),
+])
+def test_q4_0_fast_kernel_matches_oracle(ops, synth, rows, n):
+    q = synth.q4_0_weights(rows, n, 500 + rows * 3 + n)
+    x = synth.activations(n * 32, 600 + rows + n)
+    pad = np.zeros(((q.size + 31) // 16) * 16, np.uint8)   # spare tail, as any allocator gives
+    pad[:q.size] = q
+    st = ops.new_status()
+    y = ops.q4_0_matvec(dev(pad), dev(x), rows, n, status=st).cpu().numpy()
+    assert int(st.item()) == 0
+    check_fast("q4_0", y, q, x, rows, n)
+
+
+def test_q4_0_zero_blocks_writes_positive_zero(ops):
+    q = torch.zeros(32, dtype=torch.uint8, device="cuda")
+    x = torch.zeros(4, dtype=torch.float32, device="cuda")
+    y = torch.full((3,), -1.0, dtype=torch.float32, device="cuda")
+    ops.q4_0_matvec(q, x, 3, 0, y=y)
+    assert (y.cpu().numpy().view(np.uint32) == 0).all()
+
+
+# ------------------------------------------------------------------- full benchmark sizes
+
+def _full_size_check(ops, fmt, q_np, x_np, rows, n, sample_rows):
+    """Full-size run: every row against an fp64 product of the GPU's own bit-exact dequantised
+    weights (themselves checked against the oracle on a row sample), the oracle on the sample."""
+    q, x = dev(q_np), dev(x_np)
+    blk_b, blk_e = (144, 256) if fmt == "q4k" else (18, 32)
+    matvec = ops.q4k_matvec if fmt == "q4k" else ops.q4_0_matvec
+    dequant = ops.q4k_dequant if fmt == "q4k" else ops.q4_0_dequant
+    st = ops.new_status()
+    y = matvec(q, x, rows, n, status=st)
+    assert int(st.item()) == 0
+    w = dequant(q, rows, n)
+    for r in sample_rows:
+        w_ref = oracle.dequant_rows(fmt, q_np[r * n * blk_b:(r + 1) * n * blk_b], 1, n)[0]
+        assert (w[r].cpu().numpy().view(np.uint32) == w_ref.view(np.uint32)).all()
+    xd = x.double()
+    y64 = w.double() @ xd
+    mag = w.double().abs() @ xd.abs()
+    normwise = ((y.double() - y64).abs() / mag).max().item()
+    assert normwise <= NORMWISE_TOL, normwise
+    idx = np.array(sample_rows)
+    y_ref = np.array([oracle.matvec_rows(fmt, q_np[r * n * blk_b:(r + 1) * n * blk_b], x_np, 1, n)[0]
+                      for r in sample_rows])
+    got = y.cpu().numpy()[idx]
+    assert (np.abs(got - y_ref) / mag.cpu().numpy()[idx]).max() <= NORMWISE_TOL
+    # linearity: y(a*x) == a*y(x) exactly for a power of two
+    y2 = matvec(q, x * 4.0, rows, n)
+    assert torch.equal(y2, y * 4.0)
+    return y
+
+
+def test_q4k_full_size_up_gate_14336x4096(ops, synth):
+    rows, n = 14336, 16
+    q = synth.q4k_weights(rows, n, synth.config_seed(2, 0))
+    x = synth.activations(n * 256, synth.config_seed(2, 1))
+    y = _full_size_check(ops, "q4k", q, x, rows, n, [0, 1, 48, 49, 7167, 14335])
+    # strict relative figure against the oracle on a 2048-row sample, in distribution
+    rs = 2048
+    y_ref = oracle.matvec_rows("q4k", q[:rs * n * 144], x, rs, n)
+    strict = rel_err_reference_rule(y.cpu().numpy()[:rs], y_ref)
+    assert np.median(strict) < 5e-6 and (strict <= 1e-5).mean() > 0.90 and strict.max() < 1e-1
+
+
+def test_q4k_full_size_down_4096x14336(ops, synth):
+    rows, n = 4096, 56
+    q = synth.q4k_weights(rows, n, synth.config_seed(2, 2))
+    x = synth.activations(n * 256, synth.config_seed(2, 3))
+    _full_size_check(ops, "q4k", q, x, rows, n, [0, 27, 28, 2047, 4095])
+
+
+def test_q4_0_full_size_4096x4096(ops, synth):
+    rows, n = 4096, 128
+    q = synth.q4_0_weights(rows, n, synth.config_seed(1, 0))
+    x = synth.activations(n * 32, synth.config_seed(1, 1))
+    _full_size_check(ops, "q4_0", q, x, rows, n, [0, 13, 14, 2048, 4095])

@@ -1,0 +1,179 @@
+"""CPU oracle vs the reference's known-answer tests, its own second restatement and the numpy
+twin.  No GPU."""
+import hashlib
+
+import numpy as np
+import pytest
+
+import oracle
+from oracle import oracle_np
+
+
+def bits(v):
+    return int(np.float32(v).view(np.uint32))
+
+
+# ---- the reference's known-answer tests (golden, typed from its test sources) ----
+
+def test_at_1312_unpack_scale_min_k4_hand_verified_pairs(golden):
+    for case in golden["known"]["at_1312_unpack_scale_min_k4"]:
+        sc, m = oracle.unpack_scale_min_k4(case["scales"], case["j"])
+        sc2, m2 = oracle_np.unpack_scale_min_k4(case["scales"], case["j"])
+        assert (sc, m) == (sc2, m2)
+        if case["sc"] is not None:
+            assert sc == case["sc"], case
+        assert m == case["m"], case
+
+
+def test_q4_0_layout_fixtures(golden):
+    for case in golden["known"]["q4_0_layout"]:
+        q = np.array(case["q"], np.uint8)
+        x = np.array(case["x"], np.float32)
+        for fn in (oracle.q4_0_dequant_matvec_cpu, oracle.q4_0_axc_body, oracle_np.q4_0_dequant_matvec):
+            got = fn(q, x, case["n_blocks"])
+            assert abs(float(got) - case["expected"]) < case["abs_tol"], (fn.__name__, got)
+
+
+def test_q4km_zero_superblocks_is_positive_zero(golden):
+    r = oracle.q4km_dequant_matvec_cpu(np.zeros(0, np.uint8), np.zeros(0, np.float32), 0)
+    assert bits(r) == golden["known"]["q4km_n0"]["expected_bits"]
+    assert bits(oracle.q4_0_dequant_matvec_cpu(np.zeros(0, np.uint8), np.zeros(0, np.float32), 0)) == 0
+
+
+def test_reference_size_assertions():
+    q, x = oracle.generate_q4km_test_data(2, 1)
+    with pytest.raises(AssertionError):
+        oracle.q4km_dequant_matvec_cpu(q[:-1], x, 2)
+    with pytest.raises(AssertionError):
+        oracle.q4km_dequant_matvec_cpu(q, x[:-1], 2)
+    oracle.q4km_dequant_matvec_cpu(q, np.concatenate([x, x]), 2)  # x may be longer
+    q0 = np.zeros(18, np.uint8)
+    with pytest.raises(AssertionError):
+        oracle.q4_0_dequant_matvec_cpu(q0, np.zeros(33, np.float32), 1)  # x must match exactly
+
+
+# ---- the reference's reproducible LCG fixture ----
+
+def test_lcg_fixture_matches_committed_golden(golden):
+    for fx in golden["lcg"]["fixtures"]:
+        q, x = oracle.generate_q4km_test_data(fx["n_superblocks"], fx["seed"])
+        assert hashlib.sha256(q.tobytes()).hexdigest() == fx["q_sha256"]
+        assert hashlib.sha256(x.tobytes()).hexdigest() == fx["x_sha256"]
+        assert [int(v) for v in q[:16]] == fx["q_first16"]
+        y = oracle.q4km_dequant_matvec_cpu(q, x, fx["n_superblocks"])
+        assert bits(y) == fx["y_bits"]
+        w = oracle.dequant_rows("q4k", q, 1, fx["n_superblocks"])
+        assert hashlib.sha256(w.tobytes()).hexdigest() == fx["w_sha256"]
+
+
+def test_at_1323_finite_and_reproducible():
+    q, x = oracle.generate_q4km_test_data(16, 0xDEADBEEF)
+    a = oracle.q4km_dequant_matvec_cpu(q, x, 16)
+    b = oracle.q4km_dequant_matvec_cpu(q, x, 16)
+    assert np.isfinite(a) and bits(a) == bits(b)
+
+
+def test_lcg_fixture_python_twin_is_bit_identical():
+    for seed, n in ((0xDEADBEEF, 16), (0xCAFEBABE, 3), (0, 1)):
+        q, x = oracle.generate_q4km_test_data(n, seed)
+        qn, xn = oracle_np.generate_q4km_test_data(n, seed)
+        assert (q == qn).all()
+        assert (x.view(np.uint32) == xn.view(np.uint32)).all()
+        assert x.min() >= -1.0 and x.max() <= 1.0
+
+
+# ---- three restatements agree bit for bit ----
+
+@pytest.mark.parametrize("n", [1, 2, 7, 16, 128])
+def test_q4km_three_restatements_agree(n):
+    for seed in (0xDEADBEEF, 12345):
+        q, x = oracle.generate_q4km_test_data(n, seed)
+        a = oracle.q4km_dequant_matvec_cpu(q, x, n)
+        assert bits(a) == bits(oracle.q4km_axc_body(q, x, n)) == bits(oracle_np.q4km_dequant_matvec(q, x, n))
+        w = oracle.dequant_rows("q4k", q, 1, n)[0]
+        assert (w.view(np.uint32) == oracle_np.q4km_dequant_row(q, n).view(np.uint32)).all()
+
+
+@pytest.mark.parametrize("n", [1, 2, 5, 128, 1024])
+def test_q4_0_three_restatements_agree(n, synth):
+    q = synth.q4_0_weights(1, n, 42 + n)
+    x = np.random.default_rng(n).uniform(-1, 1, n * 32).astype(np.float32)
+    a = oracle.q4_0_dequant_matvec_cpu(q, x, n)
+    assert bits(a) == bits(oracle.q4_0_axc_body(q, x, n)) == bits(oracle_np.q4_0_dequant_matvec(q, x, n))
+    w = oracle.dequant_rows("q4_0", q, 1, n)[0]
+    assert (w.view(np.uint32) == oracle_np.q4_0_dequant_row(q, n).view(np.uint32)).all()
+
+
+def test_f16_widening_all_65536_and_rne_narrowing():
+    h = np.arange(65536, dtype=np.uint16)
+    ref = h.view(np.float16).astype(np.float32)
+    for v in range(0, 65536, 7):
+        f = oracle.f16_bits_to_f32(v)
+        if np.isnan(ref[v]):
+            assert np.isnan(f)
+        else:
+            assert bits(f) == bits(ref[v])
+            assert oracle.f32_to_f16_bits(f) == v
+    rng = np.random.default_rng(0)
+    vals = (rng.standard_normal(4000) * rng.choice([1e-7, 1e-5, 1e-2, 1.0, 300.0, 6e4], 4000)).astype(np.float32)
+    with np.errstate(over="ignore"):
+        expect = vals.astype(np.float16).view(np.uint16)
+    for t, e in zip(vals, expect):
+        assert oracle.f32_to_f16_bits(t) == int(e)
+
+
+# ---- rows x K generalisation, packing, synthetic distributions ----
+
+def test_rows_are_independent_reference_calls(synth):
+    rows, n = 9, 4
+    q = synth.q4k_weights(rows, n, 5)
+    x = synth.activations(n * 256, 6)
+    y1 = oracle.matvec_rows("q4k", q, x, rows, n, threads=1)
+    y4 = oracle.matvec_rows("q4k", q, x, rows, n, threads=4)
+    assert (y1.view(np.uint32) == y4.view(np.uint32)).all()
+    for r in range(rows):
+        one = oracle.q4km_dequant_matvec_cpu(q[r * n * 144:(r + 1) * n * 144], x, n)
+        assert bits(one) == bits(y1[r])
+
+
+def test_pack_scale_min_round_trips_through_unpack(synth):
+    rng = np.random.default_rng(3)
+    for _ in range(200):
+        sc = rng.integers(0, 64, 8, dtype=np.uint8)
+        m = rng.integers(0, 64, 8, dtype=np.uint8)
+        packed = oracle.pack_scale_min_k4(sc, m)
+        assert (packed == synth.pack_q4k_scales(sc, m)).all()
+        for j in range(8):
+            assert oracle.unpack_scale_min_k4(packed, j) == (int(sc[j]), int(m[j]))
+
+
+def test_synthetic_q4k_distribution(synth):
+    q = synth.q4k_weights(64, 16, 7).reshape(-1, 144)
+    d = q[:, 0:4].copy().view(np.float16).astype(np.float32)
+    assert (d >= 0).all() and 0.004 < float(d.mean()) < 0.012      # E|N(0,1)|*0.01 ~ 0.008
+    sc = np.array([[oracle.unpack_scale_min_k4(row[4:16], j) for j in range(8)] for row in q[:200]])
+    assert sc.min() >= 0 and sc.max() <= 63 and 28 < sc.mean() < 35
+    qe = synth.q4k_weights(4, 2, 7, explicit_pack=True).reshape(-1, 144)
+    assert qe.shape == (8, 144)
+
+
+def test_f64_truth_and_normwise_error_of_the_fp32_reference(synth):
+    rows, n = 64, 16
+    q = synth.q4k_weights(rows, n, 11)
+    x = synth.activations(n * 256, 12)
+    y = oracle.matvec_rows("q4k", q, x, rows, n)
+    y64, mag = oracle.matvec_rows_f64("q4k", q, x, rows, n)
+    assert (np.abs(y - y64) / mag).max() < 3e-6
+
+
+def test_prefill_oracle_matches_numpy_gemm(synth):
+    m_rows, n_rows, n_sb = 4, 6, 2
+    q = synth.q4k_weights(n_rows, n_sb, 21)
+    a = synth.activations(m_rows * n_sb * 256, 22).reshape(m_rows, -1)
+    c = oracle.q4km_prefill(q, a, m_rows, n_rows, n_sb)
+    w = oracle.dequant_rows("q4k", q, n_rows, n_sb)
+    import torch
+    wb = torch.from_numpy(w).to(torch.bfloat16).to(torch.float64).numpy()
+    ab = torch.from_numpy(a.copy()).to(torch.bfloat16).to(torch.float64).numpy()
+    ref = ab @ wb.T
+    assert np.abs(c - ref).max() / np.abs(ref).max() < 1e-5
