@@ -57,7 +57,7 @@ class AxcDispatchStats(C.Structure):
 
 class AxcTuning(C.Structure):
     _fields_ = [("ctas_per_sm", C.c_int32), ("tile_rows", C.c_int32), ("stages", C.c_int32),
-                ("threads", C.c_int32), ("evict_first", C.c_int32)]
+                ("threads", C.c_int32), ("evict_first", C.c_int32), ("pdl", C.c_int32), ("resident", C.c_int32)]
 
 
 # Every symbol include/axc_cuda.h declares: name -> (restype, argtypes)

@@ -13,6 +13,8 @@ struct MatvecTuning {
     int stages = 0;       // stages in the ring
     int threads = 0;      // threads per CTA (Q4_0 only; Q4_K derives it from the row length)
     int evict_first = -1; // L2 evict-first hint on the weight stream (-1 = default)
+    int pdl = -1;         // programmatic dependent launch: 0 off, 1 on, 2 on + weights before the wait (-1 = default)
+    int resident = 0;     // CTAs per SM the shared-memory budget is cut for (0 = default)
     int dry_run = 0;      // compute the launch geometry only, launch nothing
 };
 

@@ -410,7 +410,7 @@ axc::MatvecTuning to_tuning(const axc_tuning* t) {
     axc::MatvecTuning m;
     if (t) {
         m.ctas_per_sm = t->ctas_per_sm, m.tile_rows = t->tile_rows, m.stages = t->stages;
-        m.threads = t->threads, m.evict_first = t->evict_first;
+        m.threads = t->threads, m.evict_first = t->evict_first, m.pdl = t->pdl, m.resident = t->resident;
     }
     return m;
 }

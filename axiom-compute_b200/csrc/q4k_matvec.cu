@@ -5,15 +5,10 @@
 // row r is one reference call on the 144-byte superblocks q[r*n_sb .. (r+1)*n_sb) against the
 // shared activation vector x.
 //
-//  * q4k_matvec_stream_kernel -- the fast path.  Each CTA owns a contiguous range of rows and
-//    pulls it through a shared-memory ring with untiled bulk async copies (TMA engine), so a
-//    CTA has up to its whole share of the weight stream in flight from the first cycle.
-//    A thread owns one 64-weight chunk position (superblock s, chunk c) for the life of the
-//    CTA and keeps the 64 activations it needs in registers, pre-multiplied by powers of two
-//    so that a masked nibble, reinterpreted as a (sub)normal float, can be fed straight to a
-//    packed fp32x2 FMA: per weight one LOP3 and half an FMA instruction, no integer-to-float
-//    conversion.  Per 32-weight sub-block the dot uses the algebraically equal form
-//    d*sc*sum(q_i x_i) - dmin*m*sum(x_i); rows are reduced with warp shuffles.
+//  * q4k_matvec_segmented_kernel -- rows longer than 128 superblocks (K > 32768): the row is
+//    cut into K segments of 64 superblocks, each staged through shared memory with one bulk
+//    async copy per row, and y is accumulated over the segments.  Same arithmetic as the
+//    streaming kernel in q4k_stream.cu (which serves every shorter row and explains it).
 //  * q4k_matvec_seq_kernel -- one thread per row in the reference's exact operation order
 //    (separately rounded multiplies and adds); its y is bit-identical to the CPU reference.
 //  * q4k_dequant_kernel -- writes the dequantised weights, bit-identical to the reference's
@@ -23,7 +18,7 @@
 
 namespace axc {
 
-struct Q4kStreamParams {
+struct Q4kSegParams {
     const uint8_t* q;
     const float* x;
     float* y;
@@ -90,7 +85,7 @@ __device__ __forceinline__ float q4k_chunk_dot(const uint8_t* ptr, const ChunkCt
 }
 
 template <int PASSES>
-__global__ void __launch_bounds__(512, 1) q4k_matvec_stream_kernel(const Q4kStreamParams p) {
+__global__ void __launch_bounds__(512, 1) q4k_matvec_segmented_kernel(const Q4kSegParams p) {
     extern __shared__ __align__(128) uint8_t smem[];
     const uint32_t tid = threadIdx.x;
     const uint32_t warp = tid >> 5, lane = tid & 31;
@@ -340,12 +335,12 @@ __global__ void q4k_dequant_kernel(const uint8_t* __restrict__ q, float* __restr
 
 static int round_up8(uint32_t v) { return (int)((v + 7u) & ~7u); }
 
-cudaError_t launch_q4k_matvec(const uint8_t* q, const float* x, float* y, uint32_t rows,
-                              uint32_t n_sb, uint32_t* status, cudaStream_t stream,
-                              const MatvecTuning& tune, int sm_count, LaunchInfo* info) {
+cudaError_t launch_q4k_matvec_segmented(const uint8_t* q, const float* x, float* y, uint32_t rows,
+                                        uint32_t n_sb, uint32_t* status, cudaStream_t stream,
+                                        const MatvecTuning& tune, int sm_count, LaunchInfo* info) {
     if (rows == 0 || n_sb == 0) return cudaSuccess;  // caller handles the n = 0 case
     constexpr int kMaxSeg = 128;                     // 16 warps cover 128 superblocks (K = 32768)
-    Q4kStreamParams p{};
+    Q4kSegParams p{};
     p.q = q, p.x = x, p.y = y, p.status = status, p.rows = rows, p.n_sb = n_sb;
     const int seg = n_sb <= (uint32_t)kMaxSeg ? round_up8(n_sb) : 64;
     p.seg_sb = (uint32_t)seg;
@@ -393,11 +388,11 @@ cudaError_t launch_q4k_matvec(const uint8_t* q, const float* x, float* y, uint32
     if (grid > max_useful) grid = max_useful;
     if (grid < 1) grid = 1;
 
-    void (*kern)(Q4kStreamParams) = nullptr;
+    void (*kern)(Q4kSegParams) = nullptr;
     switch (passes) {
-        case 1: kern = q4k_matvec_stream_kernel<1>; break;
-        case 2: kern = q4k_matvec_stream_kernel<2>; break;
-        default: kern = q4k_matvec_stream_kernel<4>; break;
+        case 1: kern = q4k_matvec_segmented_kernel<1>; break;
+        case 2: kern = q4k_matvec_segmented_kernel<2>; break;
+        default: kern = q4k_matvec_segmented_kernel<4>; break;
     }
     if (!tune.dry_run) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);

@@ -33,8 +33,8 @@ def _chk(t: torch.Tensor, dtype, name: str, min_elems: int) -> int:
 
 
 def make_tuning(ctas_per_sm: int = 0, tile_rows: int = 0, stages: int = 0, threads: int = 0,
-                evict_first: int = -1) -> _ffi.AxcTuning:
-    return _ffi.AxcTuning(ctas_per_sm, tile_rows, stages, threads, evict_first)
+                evict_first: int = -1, pdl: int = 2, resident: int = 0) -> _ffi.AxcTuning:
+    return _ffi.AxcTuning(ctas_per_sm, tile_rows, stages, threads, evict_first, pdl, resident)
 
 
 def new_status(device=None) -> torch.Tensor:

@@ -301,7 +301,7 @@ def run_ours(args):
 
     # ---- end to end through the runtime layer (host buffers, dispatch_handle) ----
     e2e = None
-    if rank == 0 or world > 1:
+    if (rank == 0 or world > 1) and not args.skip_e2e:
         e2e_val, h2d, d2h = run_e2e(pkg, local_rank, weights, x_host, rows_local, args, world,
                                     dist if world > 1 else None, dev)
         e2e = {"value": round(e2e_val, 3), "unit": UNIT, "h2d_bytes_per_step": h2d,
@@ -416,6 +416,7 @@ def main():
     ap.add_argument("--scaling", choices=["weak", "strong"], default="weak")
     ap.add_argument("--no-graph", action="store_true", help="launch from the stream, no CUDA graph")
     ap.add_argument("--skip-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--skip-e2e", action="store_true", help="skip the host-buffer leg (profiling)")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)

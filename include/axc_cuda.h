@@ -200,6 +200,9 @@ typedef struct axc_tuning {
     int32_t stages;
     int32_t threads;
     int32_t evict_first; /* -1 = default */
+    int32_t pdl;         /* programmatic dependent launch: 0 off, 1 on, 2 on with the weight
+                            stream started before the dependency wait */
+    int32_t resident;    /* CTAs per SM the shared-memory budget is cut for; 0 = default */
 } axc_tuning;
 
 int axc_cuda_q4k_matvec(const void* q, const float* x, float* y, uint32_t rows,
