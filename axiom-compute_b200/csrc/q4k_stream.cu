@@ -3,30 +3,31 @@
 //
 // Replaces examples/q4km_dequant_matvec.axc:1-117 for `rows` outputs at once.
 //
-// Data movement.  A CTA owns a contiguous range of rows, i.e. one contiguous byte range of q.
-// Thread 0 starts untiled bulk async copies (TMA engine) of that range into a shared-memory
-// ring, one mbarrier per stage, before anything else happens; when the ring is as large as the
-// CTA's share (the 14336 x 4096 case: 48-49 rows = 112 KB per CTA, two CTAs per SM) the whole
-// matrix is in flight from the first cycles of the kernel and no stage is ever refilled.
-// Otherwise stages are recycled: every warp arrives on the stage's "empty" mbarrier when it has
-// read it, and the warp that observes the phase complete re-arms and refills it.  There is no
-// CTA-wide barrier in the loop; warps run ahead independently.
+// Data movement.  A CTA owns a contiguous range of rows, i.e. one contiguous byte range of q,
+// and pulls it through a shared-memory ring with untiled bulk async copies (TMA engine), one
+// mbarrier per stage.  Issuing a bulk copy costs tens of nanoseconds and never blocks, so one
+// thread requests the whole ring up front.  Stages are recycled without any CTA-wide barrier:
+// every warp arrives on the stage's "empty" mbarrier when it has read it, and the warp that
+// observes the phase complete re-arms and refills it.  With programmatic dependent launch the
+// next call's CTAs are scheduled while this call drains and fetch their first ring-full of
+// weights before `griddepcontrol.wait`; x is read and y written only after it.
 //
-// Arithmetic.  A thread owns one 64-weight chunk position (superblock s, chunk c: 32 bytes of
-// nibbles, sub-blocks 2c and 2c+1) for the life of the CTA and keeps the 64 activations it
-// needs in registers as 32 fp32 pairs, each pre-multiplied by a power of two.  The 32 bytes are
-// read as four 64-bit words; `word & 0x0000000F0000000F` (two LOP3, result already a register
-// pair) isolates the same nibble of two 32-bit halves, and those bits, read as fp32, are
-// exactly nibble * 2^(pos-149).  The pair goes straight into a packed fma.rn.f32x2 against the
-// matching activation pair: one LOP3 and half an FMA instruction per weight, no int-to-float
-// conversion, no register moves, products exact.  Per sub-block the algebraically equal form
-// d*sc*sum(q_i x_i) - dmin*m*sum(x_i) is used, so weights are never materialised here (the
-// bit-exact dequantised values come from q4k_dequant_kernel, which shares q4k_unpack_pair).
-// Row sums: transposed warp-shuffle reduction, per-warp partials in shared memory, one fixed-
-// order combine per CTA at the end (deterministic).
-//
-// With programmatic dependent launch the next call's CTAs may be scheduled while this call
-// drains; `griddepcontrol.wait` comes before x is read, the weight stream started or y written.
+// Arithmetic.  The 4-bit weights stay integers.  Per CTA the activations are quantised ONCE to
+// 23-bit signed fixed point relative to the largest |x| of each 64-column chunk (a power-of-two
+// scale: an error of at most 2^-23 of the chunk maximum per element, below what an fp32
+// accumulation of the row keeps), and the three low bytes of that integer are used as base-256
+// digits (two unsigned, the top one signed), transposed so that one 32-bit word holds one digit
+// of four neighbouring columns.  A thread owns one chunk position (superblock s, chunk c: 32
+// bytes of nibbles, sub-blocks 2c and 2c+1) for the life of the CTA and keeps its 48 digit
+// words in registers.  Per 32-bit word of nibbles: `w & 0x0F0F0F0F` is the four low nibbles as
+// bytes, `w & 0xF0F0F0F0` the four high ones times 16 (the 1/16 is folded into the scale), and
+// six dp4a (u8 x u8/s8, exact int32 accumulation) multiply them with the digit words: two
+// logic instructions and six integer-dot instructions per eight weights, nothing converted per
+// weight.  Per sub-block the exact integer sum is rescaled once and combined as
+// d*sc*sum(q_i x_i) - dmin*m*sum(x_i), so weights are never materialised here (the bit-exact
+// dequantised values come from q4k_dequant_kernel, which shares q4k_unpack_pair).  Row sums:
+// transposed warp-shuffle reduction, per-warp partials in shared memory, one fixed-order combine
+// per CTA at the end (deterministic).
 #include "axc_device.cuh"
 #include "axc_kernels.h"
 
@@ -58,11 +59,13 @@ struct Q4kStreamParams {
     uint32_t part_entries;   // capacity of the partial-sum array (>= rows per CTA * warps_per_row)
     uint32_t evict_first;
     uint32_t prefetch_first; // start the weight stream before griddepcontrol.wait
-    uint32_t x_pitch;        // positions (4 per superblock) rounded up to 8
+    uint32_t x_pitch;        // chunk positions (4 per superblock) rounded up to 8
+    uint32_t xs_offset;      // byte offset of the digit words  uint4[16][x_pitch]
+    uint32_t xm_offset;      // byte offset of the chunk metadata float4[x_pitch]
     uint32_t rows_base;      // rows / grid
     uint32_t rows_rem;       // rows % grid: the first rows_rem CTAs take one row more
     uint32_t tiles_lo, tiles_hi;  // tiles of a CTA with rows_base / rows_base + 1 rows
-    uint32_t xs_offset;      // byte offset of the staged activations in shared memory
+    uint32_t x_pos_end;      // chunk positions rounded up to a whole warp's worth (8)
 };
 
 __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
@@ -81,45 +84,53 @@ __device__ __forceinline__ bool mbar_test(uint64_t* bar, uint32_t parity) {
     return done != 0;
 }
 
-// Per-thread constants: the chunk's 64 activations as pre-scaled pairs, and the header decode
-// selectors for chunk c.
+// acc += sum_i a.u8[i] * b.s8[i]   (exact)
+__device__ __forceinline__ void dp4a_us(int& acc, uint32_t a, uint32_t b) {
+    asm("dp4a.u32.s32 %0, %1, %2, %0;" : "+r"(acc) : "r"(a), "r"(b));
+}
+// acc += sum_i a.u8[i] * b.u8[i]   (exact)
+__device__ __forceinline__ void dp4a_uu(uint32_t& acc, uint32_t a, uint32_t b) {
+    asm("dp4a.u32.u32 %0, %1, %2, %0;" : "+r"(acc) : "r"(a), "r"(b));
+}
+
+constexpr int X_FRAC_BITS = 21;  // |x| < 2^(e+1)  ->  |x * 2^(21-e)| < 2^22: top byte in [-64, 63]
+
+// Per-thread constants for the life of the CTA.
 struct LaneCtx {
-    uint64_t xl[4][4];  // [64-bit word k][byte b]: low-nibble columns (8k+b, 8k+4+b)
-    uint64_t xh[4][4];  // high-nibble columns (32+8k+b, 32+8k+4+b)
-    float x_lo_sum, x_hi_sum;
-    float rs_a, rs_b;   // 2^(149 - C) as two representable factors
-    uint32_t sh0, sh_m, sh2, mask_a, mask_b;  // scale/min unpack selectors
+    uint32_t al[8][3];  // low-nibble columns 4w..4w+3 of the chunk: digit words j = 0..2
+    uint32_t ah[8][3];  // high-nibble columns 32+4w..32+4w+3
+    float x_lo_sum, x_hi_sum;  // sum of the 32 activations of sub-block 2c / 2c+1
+    float ps_a, ps_b;          // 2^(e - 21) as two representable factors
+    uint32_t sh0, sh_m, sh2, mask_a, mask_b;  // scale/min unpack selectors for chunk c
     bool big;
 };
 
-__device__ __forceinline__ float q4k_chunk_dot64(const uint8_t* sb_ptr, uint32_t qs_off,
-                                                 const LaneCtx& t) {
+// Dot of one 64-weight chunk (32 nibble bytes at sb_ptr + qs_off) with the thread's digit words.
+// Returns this thread's contribution to the row sum.
+__device__ __forceinline__ float q4k_chunk_dot_i8(const uint8_t* sb_ptr, uint32_t qs_off,
+                                                  const LaneCtx& t) {
     const uint4 hdr = *reinterpret_cast<const uint4*>(sb_ptr);
-    const ulonglong2 qa = *reinterpret_cast<const ulonglong2*>(sb_ptr + qs_off);
-    const ulonglong2 qb = *reinterpret_cast<const ulonglong2*>(sb_ptr + qs_off + 16);
-    const uint64_t w[4] = {qa.x, qa.y, qb.x, qb.y};
+    const uint4 qa = *reinterpret_cast<const uint4*>(sb_ptr + qs_off);
+    const uint4 qb = *reinterpret_cast<const uint4*>(sb_ptr + qs_off + 16);
+    const uint32_t w[8] = {qa.x, qa.y, qa.z, qa.w, qb.x, qb.y, qb.z, qb.w};
 
-    uint64_t al0 = 0, al1 = 0, ah0 = 0, ah1 = 0;
+    uint32_t l0 = 0, l1 = 0, h0 = 0, h1 = 0;  // unsigned digits 0, 1
+    int l2 = 0, h2 = 0;                       // signed top digit
 #pragma unroll
-    for (int k = 0; k < 4; ++k) {
-        const uint64_t v = w[k];
-        const uint64_t u = v >> 8;  // byte 3 of each half down to bits 16..23
-        ffma2(al0, v & 0x0000000F0000000FULL, t.xl[k][0]);
-        ffma2(ah0, v & 0x000000F0000000F0ULL, t.xh[k][0]);
-        ffma2(al1, v & 0x00000F0000000F00ULL, t.xl[k][1]);
-        ffma2(ah1, v & 0x0000F0000000F000ULL, t.xh[k][1]);
-        ffma2(al0, v & 0x000F0000000F0000ULL, t.xl[k][2]);
-        ffma2(ah0, v & 0x00F0000000F00000ULL, t.xh[k][2]);
-        ffma2(al1, u & 0x000F0000000F0000ULL, t.xl[k][3]);
-        ffma2(ah1, u & 0x00F0000000F00000ULL, t.xh[k][3]);
+    for (int k = 0; k < 8; ++k) {
+        const uint32_t lo4 = w[k] & 0x0F0F0F0Fu;  // bytes 4k..4k+3: elements 4k..4k+3
+        const uint32_t hi4 = w[k] & 0xF0F0F0F0u;  // 16 * elements 32+4k..32+4k+3
+        dp4a_uu(l0, lo4, t.al[k][0]);
+        dp4a_uu(h0, hi4, t.ah[k][0]);
+        dp4a_uu(l1, lo4, t.al[k][1]);
+        dp4a_uu(h1, hi4, t.ah[k][1]);
+        dp4a_us(l2, lo4, t.al[k][2]);
+        dp4a_us(h2, hi4, t.ah[k][2]);
     }
-    float a0, a1, a2, a3;
-    unpack_f32x2(al0, a0, a1);
-    unpack_f32x2(al1, a2, a3);
-    const float s_lo = (a0 + a1) + (a2 + a3);  // sum(q_i x_i) * 2^(C-149), sub-block 2c
-    unpack_f32x2(ah0, a0, a1);
-    unpack_f32x2(ah1, a2, a3);
-    const float s_hi = (a0 + a1) + (a2 + a3);  // sub-block 2c+1
+    // sum(q_i X_i), X_i = d2 * 65536 + d1 * 256 + d0 (d0, d1 unsigned bytes, d2 signed).  The
+    // high-nibble sums carry the factor 16 of the unshifted nibbles.
+    const float s_lo = fmaf((float)l2, 65536.0f, (float)(l1 * 256u + l0));
+    const float s_hi = fmaf((float)h2, 4096.0f, (float)(h1 * 256u + h0) * 0.0625f);
 
     // get_scale_min_k4 for sub-blocks 2c, 2c+1 with per-lane selectors (same bits as
     // q4k_unpack_pair; crates/axc-driver/tests/common_helpers.rs:365-381).
@@ -134,8 +145,23 @@ __device__ __forceinline__ float q4k_chunk_dot64(const uint8_t* sb_ptr, uint32_t
     t1 = fmaf((float)(sc_pair >> 8), s_hi, t1);
     float t2 = (float)(m_pair & 0xFFu) * t.x_lo_sum;
     t2 = fmaf((float)(m_pair >> 8), t.x_hi_sum, t2);
-    t1 = (t1 * t.rs_a) * t.rs_b;  // back to true scale (two exact power-of-two steps)
+    t1 = (t1 * t.ps_a) * t.ps_b;  // back to the scale of x (two exact power-of-two steps)
     return fmaf(-dmin, t2, d * t1);
+}
+
+// Four activations scaled by f1 * f2 (= 2^(21-e)) and rounded to integers -> three digit words:
+// word j holds byte j of the four integers (a 4 x 4 byte transpose).
+__device__ __forceinline__ uint4 quantize_x4(const float4 v, float f1, float f2) {
+    const uint32_t x0 = (uint32_t)__float2int_rn(v.x * f1 * f2);
+    const uint32_t x1 = (uint32_t)__float2int_rn(v.y * f1 * f2);
+    const uint32_t x2 = (uint32_t)__float2int_rn(v.z * f1 * f2);
+    const uint32_t x3 = (uint32_t)__float2int_rn(v.w * f1 * f2);
+    const uint32_t t01 = __byte_perm(x0, x1, 0x5140);  // x0.b0 x1.b0 x0.b1 x1.b1
+    const uint32_t t23 = __byte_perm(x2, x3, 0x5140);
+    const uint32_t u01 = __byte_perm(x0, x1, 0x0062);  // x0.b2 x1.b2 . .
+    const uint32_t u23 = __byte_perm(x2, x3, 0x0062);
+    return make_uint4(__byte_perm(t01, t23, 0x5410), __byte_perm(t01, t23, 0x7632),
+                      __byte_perm(u01, u23, 0x5410), 0u);
 }
 
 // Sum each of the PASSES per-lane values over the warp; afterwards lane (8 * i) holds the total
@@ -178,9 +204,10 @@ __global__ void __launch_bounds__(512, 1) q4k_matvec_stream_kernel(const Q4kStre
     uint64_t* empty = full + p.stages;
     uint32_t* claim = reinterpret_cast<uint32_t*>(empty + p.stages);
     float* part = reinterpret_cast<float*>(claim + p.stages);
-    float4* xs = reinterpret_cast<float4*>(smem + p.xs_offset);  // [16][x_pitch] float4
+    uint4* xs = reinterpret_cast<uint4*>(smem + p.xs_offset);    // [16][x_pitch] digit words
+    float4* xm = reinterpret_cast<float4*>(smem + p.xm_offset);  // [x_pitch] sums and scale
 
-    // Let the next grid in the stream begin its own prologue as early as the hardware allows.
+    // Let the next grid in the stream be scheduled as early as the hardware allows.
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     TRACE(0);
 
@@ -199,7 +226,6 @@ __global__ void __launch_bounds__(512, 1) q4k_matvec_stream_kernel(const Q4kStre
     const uint32_t sb = warp_in_row * 8 + (lane >> 2);
     const uint32_t c = lane & 3;
     const bool active = sb < p.n_sb;
-    const uint32_t sb_off = sb * Q4K_SB_BYTES;
     const uint32_t qs_off = 16 + c * 32;
 
     uint64_t policy = 0;
@@ -226,7 +252,7 @@ __global__ void __launch_bounds__(512, 1) q4k_matvec_stream_kernel(const Q4kStre
     }
     __syncthreads();  // barriers are initialised for everyone
 
-    auto start_stream = [&]() {  // issuing a bulk copy takes tens of nanoseconds and never blocks
+    auto start_stream = [&]() {
         if (tid == 0) {
             const uint32_t first = min(p.stages, n_tiles);
             for (uint32_t t = 0; t < first; ++t) issue(t, t);
@@ -242,35 +268,55 @@ __global__ void __launch_bounds__(512, 1) q4k_matvec_stream_kernel(const Q4kStre
     asm volatile("griddepcontrol.wait;" ::: "memory");
     TRACE(1);
 
-    // Stage x through shared memory: coalesced 16-byte loads (each lane reading its own 256-byte
-    // chunk straight from global memory would touch 32 cache lines per instruction and serialise
-    // in L1 for microseconds), stored transposed as xs[k][position] with an XOR swizzle so that
-    // both these stores and the per-thread reads below are free of bank conflicts.
+    // Quantise x once per CTA.  Four threads share a 64-column chunk position: thread (pos, qt)
+    // loads columns 16qt..16qt+15 (coalesced across the warp), i.e. the four nibble words
+    // k = 4qt..4qt+3 of that half (qt < 2: low nibbles, qt >= 2: high nibbles), so each float4 is
+    // one dp4a operand set.  Stored as xs[k][pos] with an XOR swizzle so that these stores and the
+    // per-thread reads below are free of bank conflicts.
     {
-        const uint32_t n_vec = p.n_sb * 64;  // float4 elements of x
         const float4* xg = reinterpret_cast<const float4*>(p.x);
-        for (uint32_t g = tid; g < n_vec; g += blockDim.x) {
-            const float4 v = __ldg(xg + g);
-            const uint32_t k = g & 15u, pos = g >> 4;
-            xs[k * p.x_pitch + (pos ^ (k & 7u))] = v;
+        constexpr uint32_t FULL = 0xFFFFFFFFu;
+        const uint32_t n_pos = p.n_sb * 4;
+        const uint32_t qt = tid & 3u;
+        for (uint32_t pos = tid >> 2; pos < p.x_pos_end; pos += blockDim.x >> 2) {
+            const bool valid = pos < n_pos;
+            float4 v[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u)
+                v[u] = valid ? __ldg(xg + pos * 16 + qt * 4 + u) : make_float4(0.f, 0.f, 0.f, 0.f);
+            // largest finite |x| of the chunk (NaNs are ignored by fmaxf) and the half sums
+            float m = 0.0f, s = 0.0f;
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                m = fmaxf(m, fmaxf(fmaxf(fabsf(v[u].x), fabsf(v[u].y)), fmaxf(fabsf(v[u].z), fabsf(v[u].w))));
+                s += (v[u].x + v[u].y) + (v[u].z + v[u].w);
+            }
+            m = fmaxf(m, __shfl_xor_sync(FULL, m, 1));
+            m = fmaxf(m, __shfl_xor_sync(FULL, m, 2));
+            s += __shfl_xor_sync(FULL, s, 1);                     // sum of this 32-column half
+            const float s_other = __shfl_xor_sync(FULL, s, 2);   // sum of the other half
+            m = fminf(m, __int_as_float(0x7F7FFFFF));  // an infinite x makes the row non-finite anyway
+            int e = (int)((__float_as_uint(m) >> 23) & 0xFFu) - 127;
+            if (e < -126) e = -126;
+            const int up = X_FRAC_BITS - e;  // [-106, 147]: two representable power-of-two steps
+            const int up1 = up >> 1;
+            const float f1 = exp2i(up1), f2 = exp2i(up - up1);
+            if (valid) {
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                    const uint32_t k = qt * 4 + u;
+                    xs[k * p.x_pitch + (pos ^ (k & 7u))] = quantize_x4(v[u], f1, f2);
+                }
+                if (qt == 0) {
+                    const int dn = -up, dn1 = dn >> 1;  // e - 21 in [-147, 106]
+                    xm[pos] = make_float4(s, s_other, exp2i(dn1), exp2i(dn - dn1));
+                }
+            }
         }
     }
     if (!p.prefetch_first) start_stream();
     __syncthreads();
     TRACE(2);
-
-    float xv[64];
-    if (active) {
-        const uint32_t pos = sb * 4 + c;
-#pragma unroll
-        for (int k = 0; k < 16; ++k) {
-            const float4 v = xs[k * p.x_pitch + (pos ^ (k & 7u))];
-            xv[4 * k] = v.x, xv[4 * k + 1] = v.y, xv[4 * k + 2] = v.z, xv[4 * k + 3] = v.w;
-        }
-    } else {
-#pragma unroll
-        for (int i = 0; i < 64; ++i) xv[i] = 0.0f;
-    }
 
     LaneCtx ctx;
     {
@@ -281,55 +327,28 @@ __global__ void __launch_bounds__(512, 1) q4k_matvec_stream_kernel(const Q4kStre
         ctx.sh2 = h16 + 2;
         ctx.mask_a = ctx.big ? 0x0F0Fu : 0x3F3Fu;
         ctx.mask_b = ctx.big ? 0x3030u : 0u;
-
-        float amax = 0.0f, sl = 0.0f, sh = 0.0f;
+        const uint32_t pos = active ? sb * 4 + c : 0u;
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-            sl += xv[i];
-            sh += xv[32 + i];
+        for (int k = 0; k < 8; ++k) {
+            const uint4 a = xs[k * p.x_pitch + (pos ^ (uint32_t)k)];
+            const uint4 b = xs[(8 + k) * p.x_pitch + (pos ^ (uint32_t)k)];
+            ctx.al[k][0] = a.x, ctx.al[k][1] = a.y, ctx.al[k][2] = a.z;
+            ctx.ah[k][0] = b.x, ctx.ah[k][1] = b.y, ctx.ah[k][2] = b.z;
         }
-#pragma unroll
-        for (int i = 0; i < 64; ++i) amax = fmaxf(amax, fabsf(xv[i]));  // NaN operands are ignored
-        // An infinite |x| makes the row non-finite whatever the scaling: take the largest finite
-        // exponent so that the power-of-two factors below stay representable.
-        amax = fminf(amax, __int_as_float(0x7F7FFFFF));
-        ctx.x_lo_sum = sl;
-        ctx.x_hi_sum = sh;
-        int e = (int)((__float_as_uint(amax) >> 23) & 0xFFu) - 127;
-        if (e < -126) e = -126;
-        // nibble * 2^(pos-149) times x * 2^(C-pos) = nibble * x * 2^(C-149): about 2^-61 for the
-        // largest |x| of the chunk, far from overflow and from the subnormal range whatever the
-        // magnitude of the activations.  Both scalings are by exact powers of two.
-        const int C = 88 - e;   // [-39, 214]
-        const int C1 = C >> 1, C2 = C - C1;
-        const int R = 149 - C;  // [-65, 188]
-        const int R1 = R >> 1;
-        ctx.rs_a = exp2i(R1);
-        ctx.rs_b = exp2i(R - R1);
-        const float f1 = exp2i(C1);
-        const float gl[4] = {exp2i(C2), exp2i(C2 - 8), exp2i(C2 - 16), exp2i(C2 - 16)};
-        const float gh[4] = {exp2i(C2 - 4), exp2i(C2 - 12), exp2i(C2 - 20), exp2i(C2 - 20)};
-#pragma unroll
-        for (int k = 0; k < 4; ++k) {
-#pragma unroll
-            for (int b = 0; b < 4; ++b) {
-                ctx.xl[k][b] = pack_f32x2(xv[8 * k + b] * f1 * gl[b], xv[8 * k + 4 + b] * f1 * gl[b]);
-                ctx.xh[k][b] = pack_f32x2(xv[32 + 8 * k + b] * f1 * gh[b],
-                                          xv[32 + 8 * k + 4 + b] * f1 * gh[b]);
-            }
-        }
+        const float4 meta = xm[pos];
+        ctx.x_lo_sum = meta.x, ctx.x_hi_sum = meta.y, ctx.ps_a = meta.z, ctx.ps_b = meta.w;
     }
 
     TRACE(3);
-    // Inactive lanes (superblock index past the row) read superblock 0 and are zeroed below.
-    const uint8_t* lane_base = ring + (active ? sb_off : 0u) + row_in_pass * row_bytes;
+    // Lanes past the end of the row read superblock 0 and are zeroed below.
+    const uint8_t* lane_base = ring + (active ? sb * Q4K_SB_BYTES : 0u) + row_in_pass * row_bytes;
     const uint32_t pass_stride = p.rows_per_pass * row_bytes;
     const uint32_t wpr = p.warps_per_row;
     float* part_ptr = part + row_in_pass * wpr + warp_in_row;
     const uint32_t part_pass_stride = p.rows_per_pass * wpr;
     const uint32_t part_tile_stride = p.tile_rows * wpr;
     constexpr uint32_t kWriterStep = PASSES == 4 ? 8u : 16u;
-    const uint32_t writer_ps = lane / kWriterStep;  // which of the PASSES totals this lane ends up with
+    const uint32_t writer_ps = lane / kWriterStep;  // which of the PASSES totals this lane gets
     const bool is_writer = (lane & (kWriterStep - 1)) == 0 && writer_ps < (uint32_t)PASSES;
     const uint32_t writer_row = writer_ps * p.rows_per_pass + row_in_pass;
 
@@ -342,12 +361,12 @@ __global__ void __launch_bounds__(512, 1) q4k_matvec_stream_kernel(const Q4kStre
         float v[PASSES];
         if (rows_left >= p.tile_rows) {
 #pragma unroll
-            for (int ps = 0; ps < PASSES; ++ps) v[ps] = q4k_chunk_dot64(sp + ps * pass_stride, qs_off, ctx);
+            for (int ps = 0; ps < PASSES; ++ps) v[ps] = q4k_chunk_dot_i8(sp + ps * pass_stride, qs_off, ctx);
         } else {
 #pragma unroll
             for (int ps = 0; ps < PASSES; ++ps)
                 v[ps] = ps * p.rows_per_pass + row_in_pass < rows_left
-                            ? q4k_chunk_dot64(sp + ps * pass_stride, qs_off, ctx)
+                            ? q4k_chunk_dot_i8(sp + ps * pass_stride, qs_off, ctx)
                             : 0.0f;
         }
         if (!active) {
@@ -377,8 +396,8 @@ __global__ void __launch_bounds__(512, 1) q4k_matvec_stream_kernel(const Q4kStre
     __syncthreads();
     TRACE(19);
     for (uint32_t r = tid; r < my_rows; r += blockDim.x) {
-        float sum = part[r * p.warps_per_row];
-        for (uint32_t wv = 1; wv < p.warps_per_row; ++wv) sum += part[r * p.warps_per_row + wv];
+        float sum = part[r * wpr];
+        for (uint32_t wv = 1; wv < wpr; ++wv) sum += part[r * wpr + wv];
         p.y[r0 + r] = sum;
     }
 }
@@ -399,8 +418,8 @@ cudaError_t launch_q4k_matvec(const uint8_t* q, const float* x, float* y, uint32
     p.q = q, p.x = x, p.y = y, p.status = status, p.rows = rows, p.n_sb = n_sb;
     p.warps_per_row = (n_sb + 7) / 8;
     // CTA shape: whole rows per pass, about `threads` threads.  `ctas_per_sm` sizes the grid,
-    // `resident` the shared-memory budget (CTAs of this and of the next kernel that should fit
-    // on an SM together; about 118 registers per thread allow 16 warps per SM in total).
+    // `resident` the shared-memory budget (how many CTAs should fit on an SM together; about 118
+    // registers per thread allow 16 warps per SM in total).
     int threads = tune.threads > 0 ? tune.threads : 256;
     if (p.warps_per_row > 8) threads = 512;
     int rows_per_pass = (threads / 32) / (int)p.warps_per_row;
@@ -427,9 +446,10 @@ cudaError_t launch_q4k_matvec(const uint8_t* q, const float* x, float* y, uint32
     const size_t row_bytes = (size_t)n_sb * Q4K_SB_BYTES;
     const size_t smem_cap = (size_t)(227 * 1024) / resident - 1024;  // 1 KB per CTA is reserved
     p.x_pitch = (n_sb * 4 + 7) & ~7u;
-    const size_t xs_bytes = (size_t)16 * p.x_pitch * 16;
-    const size_t fixed = (((size_t)p.part_entries * 4 + 64 + 15) & ~(size_t)15) + xs_bytes;
-    int passes = 2;
+    const size_t xs_bytes = (size_t)16 * p.x_pitch * 16;  // digit words
+    const size_t xm_bytes = (size_t)p.x_pitch * 16;       // per-chunk sums and scale
+    const size_t fixed = (((size_t)p.part_entries * 4 + 64 + 15) & ~(size_t)15) + xs_bytes + xm_bytes;
+    int passes = 4;
     if (tune.tile_rows > 0) passes = tune.tile_rows / rows_per_pass;
     if (passes >= 4) passes = 4;
     else if (passes >= 2) passes = 2;
@@ -445,7 +465,7 @@ cudaError_t launch_q4k_matvec(const uint8_t* q, const float* x, float* y, uint32
         return ((ring + (size_t)st * 20 + 15) & ~(size_t)15) + fixed;
     };
     while (passes > 1 && smem_for(passes, 2) > smem_cap) passes >>= 1;
-    if (smem_for(passes, 1) > smem_cap) return cudaErrorInvalidConfiguration;
+    if (smem_for(passes, 1) > (size_t)227 * 1024 - 1024) return cudaErrorInvalidConfiguration;
     p.tile_rows = (uint32_t)(passes * rows_per_pass);
     p.stage_bytes = (uint32_t)(p.tile_rows * row_bytes);
     const int tiles_per_cta = tiles_for(passes);
@@ -457,7 +477,9 @@ cudaError_t launch_q4k_matvec(const uint8_t* q, const float* x, float* y, uint32
     p.stages = (uint32_t)stages;
     p.ring_bytes = (uint32_t)(stages >= tiles_per_cta ? (size_t)rows_per_cta * row_bytes
                                                       : (size_t)stages * p.stage_bytes);
-    p.xs_offset = (uint32_t)(smem - xs_bytes);
+    p.xm_offset = (uint32_t)(smem - xm_bytes);
+    p.xs_offset = (uint32_t)(smem - xm_bytes - xs_bytes);
+    p.x_pos_end = (n_sb * 4 + 7) & ~7u;
     p.rows_base = rows / grid, p.rows_rem = rows % grid;
     p.tiles_lo = (p.rows_base + p.tile_rows - 1) / p.tile_rows;
     p.tiles_hi = (p.rows_base + 1 + p.tile_rows - 1) / p.tile_rows;
