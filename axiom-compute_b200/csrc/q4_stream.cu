@@ -1,33 +1,39 @@
-// Q4_K_M dequantise + matrix-vector, streaming kernel for sm_100a (rows of up to 128
-// superblocks, i.e. K <= 32768; longer rows take the K-segmented kernel in q4k_matvec.cu).
-//
-// Replaces examples/q4km_dequant_matvec.axc:1-117 for `rows` outputs at once.
+// Streaming dequantise + matrix-vector kernel for sm_100a, both 4-bit block formats:
+//   Q4_K_M  144-byte superblocks of 256 weights  (examples/q4km_dequant_matvec.axc:1-117)
+//   Q4_0     18-byte blocks of 32 weights         (examples/q4_0_dequant_matvec.axc:1-51)
+// generalised from the reference's single output to `rows` outputs per launch: row r is one
+// reference call on the r-th run of blocks against the shared activation vector x.
+// Serves Q4_K_M rows of up to 128 superblocks and Q4_0 rows of an even number of blocks up to
+// 1024 (K <= 32768); other shapes take the kernels in q4k_matvec.cu / q4_0_matvec.cu.
 //
 // Data movement.  A CTA owns a contiguous range of rows, i.e. one contiguous byte range of q,
 // and pulls it through a shared-memory ring with untiled bulk async copies (TMA engine), one
 // mbarrier per stage.  Issuing a bulk copy costs tens of nanoseconds and never blocks, so one
 // thread requests the whole ring up front.  Stages are recycled without any CTA-wide barrier:
 // every warp arrives on the stage's "empty" mbarrier when it has read it, and the warp that
-// observes the phase complete re-arms and refills it.  With programmatic dependent launch the
-// next call's CTAs are scheduled while this call drains and fetch their first ring-full of
-// weights before `griddepcontrol.wait`; x is read and y written only after it.
+// observes the phase complete re-arms and refills it.  (18-byte Q4_0 blocks are only 2-byte
+// aligned: a tile is copied as the enclosing 16-byte aligned range and addressed with the
+// remainder.)  With programmatic dependent launch the next call's CTAs are scheduled while this
+// call drains and fetch their first ring-full of weights before `griddepcontrol.wait`; x is
+// read and y written only after it.
 //
 // Arithmetic.  The 4-bit weights stay integers.  Per CTA the activations are quantised ONCE to
 // 23-bit signed fixed point relative to the largest |x| of each 64-column chunk (a power-of-two
 // scale: an error of at most 2^-23 of the chunk maximum per element, below what an fp32
 // accumulation of the row keeps), and the three low bytes of that integer are used as base-256
 // digits (two unsigned, the top one signed), transposed so that one 32-bit word holds one digit
-// of four neighbouring columns.  A thread owns one chunk position (superblock s, chunk c: 32
-// bytes of nibbles, sub-blocks 2c and 2c+1) for the life of the CTA and keeps its 48 digit
-// words in registers.  Per 32-bit word of nibbles: `w & 0x0F0F0F0F` is the four low nibbles as
-// bytes, `w & 0xF0F0F0F0` the four high ones times 16 (the 1/16 is folded into the scale), and
-// six dp4a (u8 x u8/s8, exact int32 accumulation) multiply them with the digit words: two
-// logic instructions and six integer-dot instructions per eight weights, nothing converted per
-// weight.  Per sub-block the exact integer sum is rescaled once and combined as
-// d*sc*sum(q_i x_i) - dmin*m*sum(x_i), so weights are never materialised here (the bit-exact
-// dequantised values come from q4k_dequant_kernel, which shares q4k_unpack_pair).  Row sums:
-// transposed warp-shuffle reduction, per-warp partials in shared memory, one fixed-order combine
-// per CTA at the end (deterministic).
+// of four neighbouring columns.  A thread owns one 64-weight position of the row (Q4_K_M:
+// superblock s, chunk c = 32 nibble bytes, sub-blocks 2c and 2c+1; Q4_0: a pair of blocks) for
+// the life of the CTA and keeps its 48 digit words in registers.  Per 32-bit word of nibbles:
+// `w & 0x0F0F0F0F` is the four low nibbles as bytes, `w & 0xF0F0F0F0` the four high ones times
+// 16 (the 1/16 is folded into the scale), and six dp4a (u8 x u8/s8, exact int32 accumulation)
+// multiply them with the digit words: two logic instructions and six integer-dot instructions
+// per eight weights, nothing converted per weight.  Per sub-block the exact integer sum is
+// rescaled once and combined as d*sc*sum(q_i x_i) - dmin*m*sum(x_i) (Q4_0: d*(sum(q_i x_i) -
+// 8*sum(x_i))), so weights are never materialised here (the bit-exact dequantised values come
+// from the dequant kernels, which share the unpack code).  Row sums: transposed warp-shuffle
+// reduction, per-warp partials in shared memory, one fixed-order combine per CTA at the end
+// (deterministic).
 #include "axc_device.cuh"
 #include "axc_kernels.h"
 
@@ -43,29 +49,32 @@ extern "C" int axc_debug_copy_trace(unsigned long long* dst, int n) {
 
 namespace axc {
 
-struct Q4kStreamParams {
+constexpr int FMT_Q4K = 0, FMT_Q4_0 = 1;
+
+struct StreamParams {
     const uint8_t* q;
     const float* x;
     float* y;
     uint32_t* status;
     uint32_t rows;
-    uint32_t n_sb;
-    uint32_t warps_per_row;  // ceil(n_sb / 8)
+    uint32_t row_bytes;      // bytes of q per row
+    uint32_t n_pos;          // 64-weight positions per row (Q4_K_M: 4 per superblock; Q4_0: blocks / 2)
+    uint32_t warps_per_row;  // ceil(n_pos / 32)
     uint32_t rows_per_pass;  // warps per CTA / warps_per_row
     uint32_t tile_rows;      // PASSES * rows_per_pass
     uint32_t stages;
-    uint32_t stage_bytes;    // tile_rows * n_sb * 144
+    uint32_t stage_bytes;    // capacity of one stage
     uint32_t ring_bytes;     // stages * stage_bytes, or the CTA's exact share when all resident
     uint32_t part_entries;   // capacity of the partial-sum array (>= rows per CTA * warps_per_row)
     uint32_t evict_first;
     uint32_t prefetch_first; // start the weight stream before griddepcontrol.wait
-    uint32_t x_pitch;        // chunk positions (4 per superblock) rounded up to 8
+    uint32_t x_pitch;        // positions rounded up to 8
     uint32_t xs_offset;      // byte offset of the digit words  uint4[16][x_pitch]
-    uint32_t xm_offset;      // byte offset of the chunk metadata float4[x_pitch]
+    uint32_t xm_offset;      // byte offset of the position metadata float4[x_pitch]
     uint32_t rows_base;      // rows / grid
     uint32_t rows_rem;       // rows % grid: the first rows_rem CTAs take one row more
     uint32_t tiles_lo, tiles_hi;  // tiles of a CTA with rows_base / rows_base + 1 rows
-    uint32_t x_pos_end;      // chunk positions rounded up to a whole warp's worth (8)
+    uint32_t x_pos_end;      // positions rounded up to a whole warp's worth (8)
 };
 
 __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
@@ -97,40 +106,45 @@ constexpr int X_FRAC_BITS = 21;  // |x| < 2^(e+1)  ->  |x * 2^(21-e)| < 2^22: to
 
 // Per-thread constants for the life of the CTA.
 struct LaneCtx {
-    uint32_t al[8][3];  // low-nibble columns 4w..4w+3 of the chunk: digit words j = 0..2
-    uint32_t ah[8][3];  // high-nibble columns 32+4w..32+4w+3
-    float x_lo_sum, x_hi_sum;  // sum of the 32 activations of sub-block 2c / 2c+1
-    float ps_a, ps_b;          // 2^(e - 21) as two representable factors
-    uint32_t sh0, sh_m, sh2, mask_a, mask_b;  // scale/min unpack selectors for chunk c
+    uint32_t dg[16][3];  // digit words of columns 4k..4k+3 of the position, k = 0..15
+    float sum_a, sum_b;  // sum of x over columns 0..31 / 32..63 of the position
+    float ps_a, ps_b;    // 2^(e - 21) as two representable factors
+    uint32_t sh0, sh_m, sh2, mask_a, mask_b;  // Q4_K_M scale/min unpack selectors for chunk c
     bool big;
 };
 
-// Dot of one 64-weight chunk (32 nibble bytes at sb_ptr + qs_off) with the thread's digit words.
-// Returns this thread's contribution to the row sum.
-__device__ __forceinline__ float q4k_chunk_dot_i8(const uint8_t* sb_ptr, uint32_t qs_off,
-                                                  const LaneCtx& t) {
+// Exact integer dot of four nibble words with the digit words of columns [4*k0, 4*k0 + 16):
+// low nibbles against dg[k0 + j], high nibbles (left unshifted: times 16) against dg[k1 + j].
+struct DigitSums {
+    uint32_t l0 = 0, l1 = 0, h0 = 0, h1 = 0;  // unsigned digits 0, 1
+    int l2 = 0, h2 = 0;                       // signed top digit
+    __device__ __forceinline__ void add(uint32_t w, const uint32_t (&lo)[3], const uint32_t (&hi)[3]) {
+        const uint32_t lo4 = w & 0x0F0F0F0Fu, hi4 = w & 0xF0F0F0F0u;
+        dp4a_uu(l0, lo4, lo[0]);
+        dp4a_uu(h0, hi4, hi[0]);
+        dp4a_uu(l1, lo4, lo[1]);
+        dp4a_uu(h1, hi4, hi[1]);
+        dp4a_us(l2, lo4, lo[2]);
+        dp4a_us(h2, hi4, hi[2]);
+    }
+    // sum(q_i X_i), X_i = d2 * 65536 + d1 * 256 + d0
+    __device__ __forceinline__ float low() const { return fmaf((float)l2, 65536.0f, (float)(l1 * 256u + l0)); }
+    __device__ __forceinline__ float high() const {  // carries the factor 16 of the unshifted nibbles
+        return fmaf((float)h2, 4096.0f, (float)(h1 * 256u + h0) * 0.0625f);
+    }
+};
+
+// Q4_K_M: this thread's contribution to the row sum from one superblock (chunk c of it).
+__device__ __forceinline__ float q4k_pos_dot(const uint8_t* sb_ptr, uint32_t qs_off, const LaneCtx& t) {
     const uint4 hdr = *reinterpret_cast<const uint4*>(sb_ptr);
     const uint4 qa = *reinterpret_cast<const uint4*>(sb_ptr + qs_off);
     const uint4 qb = *reinterpret_cast<const uint4*>(sb_ptr + qs_off + 16);
     const uint32_t w[8] = {qa.x, qa.y, qa.z, qa.w, qb.x, qb.y, qb.z, qb.w};
-
-    uint32_t l0 = 0, l1 = 0, h0 = 0, h1 = 0;  // unsigned digits 0, 1
-    int l2 = 0, h2 = 0;                       // signed top digit
+    // byte l of the chunk: low nibble -> element l (columns 0..31), high nibble -> element 32 + l
+    DigitSums s;
 #pragma unroll
-    for (int k = 0; k < 8; ++k) {
-        const uint32_t lo4 = w[k] & 0x0F0F0F0Fu;  // bytes 4k..4k+3: elements 4k..4k+3
-        const uint32_t hi4 = w[k] & 0xF0F0F0F0u;  // 16 * elements 32+4k..32+4k+3
-        dp4a_uu(l0, lo4, t.al[k][0]);
-        dp4a_uu(h0, hi4, t.ah[k][0]);
-        dp4a_uu(l1, lo4, t.al[k][1]);
-        dp4a_uu(h1, hi4, t.ah[k][1]);
-        dp4a_us(l2, lo4, t.al[k][2]);
-        dp4a_us(h2, hi4, t.ah[k][2]);
-    }
-    // sum(q_i X_i), X_i = d2 * 65536 + d1 * 256 + d0 (d0, d1 unsigned bytes, d2 signed).  The
-    // high-nibble sums carry the factor 16 of the unshifted nibbles.
-    const float s_lo = fmaf((float)l2, 65536.0f, (float)(l1 * 256u + l0));
-    const float s_hi = fmaf((float)h2, 4096.0f, (float)(h1 * 256u + h0) * 0.0625f);
+    for (int k = 0; k < 8; ++k) s.add(w[k], t.dg[k], t.dg[8 + k]);
+    const float s_lo = s.low(), s_hi = s.high();
 
     // get_scale_min_k4 for sub-blocks 2c, 2c+1 with per-lane selectors (same bits as
     // q4k_unpack_pair; crates/axc-driver/tests/common_helpers.rs:365-381).
@@ -143,10 +157,33 @@ __device__ __forceinline__ float q4k_chunk_dot_i8(const uint8_t* sb_ptr, uint32_
     // d * (sc0 * S_lo + sc1 * S_hi) - dmin * (m0 * sum_lo(x) + m1 * sum_hi(x))
     float t1 = (float)(sc_pair & 0xFFu) * s_lo;
     t1 = fmaf((float)(sc_pair >> 8), s_hi, t1);
-    float t2 = (float)(m_pair & 0xFFu) * t.x_lo_sum;
-    t2 = fmaf((float)(m_pair >> 8), t.x_hi_sum, t2);
+    float t2 = (float)(m_pair & 0xFFu) * t.sum_a;
+    t2 = fmaf((float)(m_pair >> 8), t.sum_b, t2);
     t1 = (t1 * t.ps_a) * t.ps_b;  // back to the scale of x (two exact power-of-two steps)
     return fmaf(-dmin, t2, d * t1);
+}
+
+// Q4_0: contribution of one block pair (36 bytes, 4-byte aligned).  Block b: fp16 d, then 16
+// bytes; byte k: low nibble -> element k, high nibble -> element k + 16
+// (crates/axc-driver/benches/common.rs:240-255).
+__device__ __forceinline__ float q40_pos_dot(const uint8_t* pair_ptr, const LaneCtx& t) {
+    const uint32_t* wp = reinterpret_cast<const uint32_t*>(pair_ptr);
+    uint32_t W[9];
+#pragma unroll
+    for (int i = 0; i < 9; ++i) W[i] = wp[i];
+    DigitSums s0, s1;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        // block 0: its 16 nibble bytes straddle the words by 16 bits
+        s0.add(__funnelshift_r(W[j], W[j + 1], 16), t.dg[j], t.dg[4 + j]);
+        s1.add(W[5 + j], t.dg[8 + j], t.dg[12 + j]);
+    }
+    const float d0 = f16_bits_to_f32(W[0] & 0xFFFFu);
+    const float d1 = f16_bits_to_f32(W[4] >> 16);
+    // d * (sum(q_i x_i) - 8 * sum(x_i)) per block
+    const float a0 = ((s0.low() + s0.high()) * t.ps_a) * t.ps_b;
+    const float a1 = ((s1.low() + s1.high()) * t.ps_a) * t.ps_b;
+    return fmaf(d1, fmaf(-8.0f, t.sum_b, a1), d0 * fmaf(-8.0f, t.sum_a, a0));
 }
 
 // Four activations scaled by f1 * f2 (= 2^(21-e)) and rounded to integers -> three digit words:
@@ -192,8 +229,8 @@ __device__ __forceinline__ float warp_reduce_transposed(const float (&v)[PASSES]
     return r;
 }
 
-template <int PASSES>
-__global__ void __launch_bounds__(512, 1) q4k_matvec_stream_kernel(const Q4kStreamParams p) {
+template <int FMT, int PASSES>
+__global__ void __launch_bounds__(512, 1) q4_matvec_stream_kernel(const StreamParams p) {
     extern __shared__ __align__(128) uint8_t smem[];
     const uint32_t tid = threadIdx.x;
     const uint32_t warp = tid >> 5, lane = tid & 31;
@@ -219,13 +256,13 @@ __global__ void __launch_bounds__(512, 1) q4k_matvec_stream_kernel(const Q4kStre
     const uint32_t r1 = r0 + my_rows;
     if (my_rows == 0) return;
     const uint32_t n_tiles = bid < p.rows_rem ? p.tiles_hi : p.tiles_lo;
-    const uint32_t row_bytes = p.n_sb * Q4K_SB_BYTES;
+    const uint32_t row_bytes = p.row_bytes;
 
     const uint32_t row_in_pass = warp / p.warps_per_row;
     const uint32_t warp_in_row = warp - row_in_pass * p.warps_per_row;
-    const uint32_t sb = warp_in_row * 8 + (lane >> 2);
-    const uint32_t c = lane & 3;
-    const bool active = sb < p.n_sb;
+    const uint32_t my_pos = warp_in_row * 32 + lane;  // this thread's 64-weight position in the row
+    const bool active = my_pos < p.n_pos;
+    const uint32_t c = lane & 3;                      // Q4_K_M: chunk within the superblock
     const uint32_t qs_off = 16 + c * 32;
 
     uint64_t policy = 0;
@@ -234,12 +271,15 @@ __global__ void __launch_bounds__(512, 1) q4k_matvec_stream_kernel(const Q4kStre
     auto issue = [&](uint32_t tile, uint32_t s) {  // one thread: arm stage s, start tile's copy
         const uint32_t row_begin = r0 + tile * p.tile_rows;
         const uint32_t nrows = min(p.tile_rows, r1 - row_begin);
-        const uint32_t bytes = nrows * row_bytes;
-        const uint8_t* src = p.q + (size_t)row_begin * row_bytes;
+        // The enclosing 16-byte aligned range (Q4_K_M rows are already aligned).  It stays inside
+        // the 16-byte granules that hold valid bytes, so it never leaves the pages of q.
+        const size_t start = (size_t)row_begin * row_bytes;
+        const size_t a_start = start & ~(size_t)15;
+        const uint32_t bytes = (uint32_t)(((start + (size_t)nrows * row_bytes + 15) & ~(size_t)15) - a_start);
         uint8_t* dst = ring + (size_t)s * p.stage_bytes;
         mbar_expect_tx(&full[s], bytes);
-        if (p.evict_first) bulk_g2s_stream(dst, src, bytes, &full[s], policy);
-        else bulk_g2s(dst, src, bytes, &full[s]);
+        if (p.evict_first) bulk_g2s_stream(dst, p.q + a_start, bytes, &full[s], policy);
+        else bulk_g2s(dst, p.q + a_start, bytes, &full[s]);
     };
 
     if (tid == 0) {
@@ -276,7 +316,7 @@ __global__ void __launch_bounds__(512, 1) q4k_matvec_stream_kernel(const Q4kStre
     {
         const float4* xg = reinterpret_cast<const float4*>(p.x);
         constexpr uint32_t FULL = 0xFFFFFFFFu;
-        const uint32_t n_pos = p.n_sb * 4;
+        const uint32_t n_pos = p.n_pos;
         const uint32_t qt = tid & 3u;
         for (uint32_t pos = tid >> 2; pos < p.x_pos_end; pos += blockDim.x >> 2) {
             const bool valid = pos < n_pos;
@@ -327,21 +367,23 @@ __global__ void __launch_bounds__(512, 1) q4k_matvec_stream_kernel(const Q4kStre
         ctx.sh2 = h16 + 2;
         ctx.mask_a = ctx.big ? 0x0F0Fu : 0x3F3Fu;
         ctx.mask_b = ctx.big ? 0x3030u : 0u;
-        const uint32_t pos = active ? sb * 4 + c : 0u;
+        const uint32_t pos = active ? my_pos : 0u;
 #pragma unroll
-        for (int k = 0; k < 8; ++k) {
-            const uint4 a = xs[k * p.x_pitch + (pos ^ (uint32_t)k)];
-            const uint4 b = xs[(8 + k) * p.x_pitch + (pos ^ (uint32_t)k)];
-            ctx.al[k][0] = a.x, ctx.al[k][1] = a.y, ctx.al[k][2] = a.z;
-            ctx.ah[k][0] = b.x, ctx.ah[k][1] = b.y, ctx.ah[k][2] = b.z;
+        for (int k = 0; k < 16; ++k) {
+            const uint4 a = xs[k * p.x_pitch + (pos ^ (uint32_t)(k & 7))];
+            ctx.dg[k][0] = a.x, ctx.dg[k][1] = a.y, ctx.dg[k][2] = a.z;
         }
         const float4 meta = xm[pos];
-        ctx.x_lo_sum = meta.x, ctx.x_hi_sum = meta.y, ctx.ps_a = meta.z, ctx.ps_b = meta.w;
+        ctx.sum_a = meta.x, ctx.sum_b = meta.y, ctx.ps_a = meta.z, ctx.ps_b = meta.w;
     }
 
     TRACE(3);
-    // Lanes past the end of the row read superblock 0 and are zeroed below.
-    const uint8_t* lane_base = ring + (active ? sb * Q4K_SB_BYTES : 0u) + row_in_pass * row_bytes;
+    // Lanes past the end of the row read position 0 and are zeroed below.
+    const uint32_t pos_off = !active ? 0u : FMT == FMT_Q4K ? (my_pos >> 2) * Q4K_SB_BYTES : my_pos * 36u;
+    const uint8_t* lane_base = ring + pos_off + row_in_pass * row_bytes;
+    // Offset of the tile's first byte inside its 16-byte aligned copy (always 0 for Q4_K_M).
+    uint32_t delta = (r0 * row_bytes) & 15u;
+    const uint32_t delta_step = (p.tile_rows * row_bytes) & 15u;
     const uint32_t pass_stride = p.rows_per_pass * row_bytes;
     const uint32_t wpr = p.warps_per_row;
     float* part_ptr = part + row_in_pass * wpr + warp_in_row;
@@ -356,18 +398,20 @@ __global__ void __launch_bounds__(512, 1) q4k_matvec_stream_kernel(const Q4kStre
     for (uint32_t tile = 0; tile < n_tiles; ++tile) {
         if (!mbar_wait(&full[s], parity, p.status)) break;  // status word set; y stays partial
         if (tile < 14) TRACE(4 + tile);
-        const uint8_t* sp = lane_base + s * p.stage_bytes;
+        const uint8_t* sp = lane_base + s * p.stage_bytes + delta;
 
         float v[PASSES];
         if (rows_left >= p.tile_rows) {
 #pragma unroll
-            for (int ps = 0; ps < PASSES; ++ps) v[ps] = q4k_chunk_dot_i8(sp + ps * pass_stride, qs_off, ctx);
+            for (int ps = 0; ps < PASSES; ++ps)
+                v[ps] = FMT == FMT_Q4K ? q4k_pos_dot(sp + ps * pass_stride, qs_off, ctx)
+                                       : q40_pos_dot(sp + ps * pass_stride, ctx);
         } else {
 #pragma unroll
             for (int ps = 0; ps < PASSES; ++ps)
-                v[ps] = ps * p.rows_per_pass + row_in_pass < rows_left
-                            ? q4k_chunk_dot_i8(sp + ps * pass_stride, qs_off, ctx)
-                            : 0.0f;
+                v[ps] = ps * p.rows_per_pass + row_in_pass >= rows_left ? 0.0f
+                        : FMT == FMT_Q4K ? q4k_pos_dot(sp + ps * pass_stride, qs_off, ctx)
+                                         : q40_pos_dot(sp + ps * pass_stride, ctx);
         }
         if (!active) {
 #pragma unroll
@@ -389,6 +433,7 @@ __global__ void __launch_bounds__(512, 1) q4k_matvec_stream_kernel(const Q4kStre
         }
         part_ptr += part_tile_stride;
         rows_left = rows_left > p.tile_rows ? rows_left - p.tile_rows : 0u;
+        delta = (delta + delta_step) & 15u;
         if (++s == p.stages) s = 0, parity ^= 1u;
     }
 
@@ -404,27 +449,24 @@ __global__ void __launch_bounds__(512, 1) q4k_matvec_stream_kernel(const Q4kStre
 
 // ---------------------------------------------------------------------------------------------
 
-cudaError_t launch_q4k_matvec_segmented(const uint8_t* q, const float* x, float* y, uint32_t rows,
-                                        uint32_t n_sb, uint32_t* status, cudaStream_t stream,
-                                        const MatvecTuning& tune, int sm_count, LaunchInfo* info);
-
-cudaError_t launch_q4k_matvec(const uint8_t* q, const float* x, float* y, uint32_t rows,
-                              uint32_t n_sb, uint32_t* status, cudaStream_t stream,
-                              const MatvecTuning& tune, int sm_count, LaunchInfo* info) {
-    if (rows == 0 || n_sb == 0) return cudaSuccess;
-    if (n_sb > 128) return launch_q4k_matvec_segmented(q, x, y, rows, n_sb, status, stream, tune, sm_count, info);
-
-    Q4kStreamParams p{};
-    p.q = q, p.x = x, p.y = y, p.status = status, p.rows = rows, p.n_sb = n_sb;
-    p.warps_per_row = (n_sb + 7) / 8;
+template <int FMT>
+static cudaError_t launch_stream(const uint8_t* q, const float* x, float* y, uint32_t rows,
+                                 uint32_t row_bytes, uint32_t n_pos, uint32_t* status,
+                                 cudaStream_t stream, const MatvecTuning& tune, int sm_count,
+                                 LaunchInfo* info) {
+    StreamParams p{};
+    p.q = q, p.x = x, p.y = y, p.status = status, p.rows = rows;
+    p.row_bytes = row_bytes, p.n_pos = n_pos;
+    p.warps_per_row = (n_pos + 31) / 32;
     // CTA shape: whole rows per pass, about `threads` threads.  `ctas_per_sm` sizes the grid,
-    // `resident` the shared-memory budget (how many CTAs should fit on an SM together; about 118
+    // `resident` the shared-memory budget (how many CTAs should fit on an SM together; about 120
     // registers per thread allow 16 warps per SM in total).
     int threads = tune.threads > 0 ? tune.threads : 256;
     if (p.warps_per_row > 8) threads = 512;
     int rows_per_pass = (threads / 32) / (int)p.warps_per_row;
     if (rows_per_pass < 1) rows_per_pass = 1;
     const int warps = rows_per_pass * (int)p.warps_per_row;
+    if (warps > 16) return cudaErrorInvalidConfiguration;
     p.rows_per_pass = (uint32_t)rows_per_pass;
     const int max_resident = 16 / warps > 0 ? 16 / warps : 1;
     int ctas_per_sm = tune.ctas_per_sm > 0 ? tune.ctas_per_sm : max_resident;
@@ -443,31 +485,38 @@ cudaError_t launch_q4k_matvec(const uint8_t* q, const float* x, float* y, uint32
     const uint32_t rows_per_cta = (rows + grid - 1) / grid;
     p.part_entries = rows_per_cta * p.warps_per_row;
 
-    const size_t row_bytes = (size_t)n_sb * Q4K_SB_BYTES;
     const size_t smem_cap = (size_t)(227 * 1024) / resident - 1024;  // 1 KB per CTA is reserved
-    p.x_pitch = (n_sb * 4 + 7) & ~7u;
+    p.x_pitch = (n_pos + 7) & ~7u;
     const size_t xs_bytes = (size_t)16 * p.x_pitch * 16;  // digit words
-    const size_t xm_bytes = (size_t)p.x_pitch * 16;       // per-chunk sums and scale
+    const size_t xm_bytes = (size_t)p.x_pitch * 16;       // per-position sums and scale
     const size_t fixed = (((size_t)p.part_entries * 4 + 64 + 15) & ~(size_t)15) + xs_bytes + xm_bytes;
     int passes = 4;
     if (tune.tile_rows > 0) passes = tune.tile_rows / rows_per_pass;
     if (passes >= 4) passes = 4;
     else if (passes >= 2) passes = 2;
     else passes = 1;
-    // Ring size: `st` stages of `ps` passes; when every tile of the CTA has its own stage the
-    // last (partial) tile only needs its own rows, so the ring is exactly the CTA's share.
+    // Stage capacity: Q4_K_M rows are multiples of 16 bytes; a Q4_0 tile is copied as its
+    // enclosing aligned range (up to 15 bytes before and after).
+    auto stage_for = [&](int ps) {
+        const size_t raw = (size_t)ps * rows_per_pass * row_bytes;
+        return FMT == FMT_Q4K ? raw : ((raw + 15) & ~(size_t)15) + 16;
+    };
     auto tiles_for = [&](int ps) {
         return (int)((rows_per_cta + (uint32_t)(ps * rows_per_pass) - 1) / (uint32_t)(ps * rows_per_pass));
     };
+    // Ring: `st` stages; when every Q4_K_M tile of the CTA has its own stage the last (partial)
+    // tile only needs its own rows, so the ring is exactly the CTA's share.
+    auto ring_for = [&](int ps, int st) {
+        if (FMT == FMT_Q4K && st >= tiles_for(ps)) return (size_t)rows_per_cta * row_bytes;
+        return (size_t)st * stage_for(ps);
+    };
     auto smem_for = [&](int ps, int st) {
-        const size_t stage = (size_t)ps * rows_per_pass * row_bytes;
-        const size_t ring = st >= tiles_for(ps) ? (size_t)rows_per_cta * row_bytes : (size_t)st * stage;
-        return ((ring + (size_t)st * 20 + 15) & ~(size_t)15) + fixed;
+        return ((ring_for(ps, st) + (size_t)st * 20 + 15) & ~(size_t)15) + fixed;
     };
     while (passes > 1 && smem_for(passes, 2) > smem_cap) passes >>= 1;
     if (smem_for(passes, 1) > (size_t)227 * 1024 - 1024) return cudaErrorInvalidConfiguration;
     p.tile_rows = (uint32_t)(passes * rows_per_pass);
-    p.stage_bytes = (uint32_t)(p.tile_rows * row_bytes);
+    p.stage_bytes = (uint32_t)stage_for(passes);
     const int tiles_per_cta = tiles_for(passes);
     int stages = tune.stages > 0 ? tune.stages : tiles_per_cta;  // whole share resident if it fits
     if (stages > tiles_per_cta) stages = tiles_per_cta;
@@ -475,26 +524,25 @@ cudaError_t launch_q4k_matvec(const uint8_t* q, const float* x, float* y, uint32
     while (stages > 1 && smem_for(passes, stages) > smem_cap) --stages;
     const size_t smem = smem_for(passes, stages);
     p.stages = (uint32_t)stages;
-    p.ring_bytes = (uint32_t)(stages >= tiles_per_cta ? (size_t)rows_per_cta * row_bytes
-                                                      : (size_t)stages * p.stage_bytes);
+    p.ring_bytes = (uint32_t)ring_for(passes, stages);
     p.xm_offset = (uint32_t)(smem - xm_bytes);
     p.xs_offset = (uint32_t)(smem - xm_bytes - xs_bytes);
-    p.x_pos_end = (n_sb * 4 + 7) & ~7u;
+    p.x_pos_end = (n_pos + 7) & ~7u;
     p.rows_base = rows / grid, p.rows_rem = rows % grid;
     p.tiles_lo = (p.rows_base + p.tile_rows - 1) / p.tile_rows;
     p.tiles_hi = (p.rows_base + 1 + p.tile_rows - 1) / p.tile_rows;
     p.evict_first = tune.evict_first > 0 ? 1u : 0u;
     p.prefetch_first = tune.pdl == 2 || tune.pdl < 0 ? 1u : 0u;
 
-    void (*kern)(Q4kStreamParams) = nullptr;
+    void (*kern)(StreamParams) = nullptr;
     switch (passes) {
-        case 1: kern = q4k_matvec_stream_kernel<1>; break;
-        case 2: kern = q4k_matvec_stream_kernel<2>; break;
-        default: kern = q4k_matvec_stream_kernel<4>; break;
+        case 1: kern = q4_matvec_stream_kernel<FMT, 1>; break;
+        case 2: kern = q4_matvec_stream_kernel<FMT, 2>; break;
+        default: kern = q4_matvec_stream_kernel<FMT, 4>; break;
     }
     if (info) {
         info->grid = (int)grid, info->block = warps * 32, info->smem = smem;
-        info->tile_rows = (int)p.tile_rows, info->stages = stages, info->seg = (int)n_sb;
+        info->tile_rows = (int)p.tile_rows, info->stages = stages, info->seg = (int)n_pos;
         info->n_seg = 1;
     }
     if (tune.dry_run) return cudaSuccess;
@@ -510,6 +558,28 @@ cudaError_t launch_q4k_matvec(const uint8_t* q, const float* x, float* y, uint32
     cfg.attrs = attr;
     cfg.numAttrs = tune.pdl != 0 ? 1 : 0;
     return cudaLaunchKernelEx(&cfg, kern, p);
+}
+
+cudaError_t launch_q4k_matvec_segmented(const uint8_t* q, const float* x, float* y, uint32_t rows,
+                                        uint32_t n_sb, uint32_t* status, cudaStream_t stream,
+                                        const MatvecTuning& tune, int sm_count, LaunchInfo* info);
+cudaError_t launch_q4_0_matvec_rowwarp(const uint8_t* q, const float* x, float* y, uint32_t rows,
+                                       uint32_t n_blocks, cudaStream_t stream, LaunchInfo* info);
+
+cudaError_t launch_q4k_matvec(const uint8_t* q, const float* x, float* y, uint32_t rows,
+                              uint32_t n_sb, uint32_t* status, cudaStream_t stream,
+                              const MatvecTuning& tune, int sm_count, LaunchInfo* info) {
+    if (rows == 0 || n_sb == 0) return cudaSuccess;
+    if (n_sb > 128) return launch_q4k_matvec_segmented(q, x, y, rows, n_sb, status, stream, tune, sm_count, info);
+    return launch_stream<FMT_Q4K>(q, x, y, rows, n_sb * Q4K_SB_BYTES, n_sb * 4, status, stream, tune, sm_count, info);
+}
+
+cudaError_t launch_q4_0_matvec(const uint8_t* q, const float* x, float* y, uint32_t rows,
+                               uint32_t n_blocks, uint32_t* status, cudaStream_t stream,
+                               const MatvecTuning& tune, int sm_count, LaunchInfo* info) {
+    if (rows == 0 || n_blocks == 0) return cudaSuccess;
+    if ((n_blocks & 1u) || n_blocks > 1024u) return launch_q4_0_matvec_rowwarp(q, x, y, rows, n_blocks, stream, info);
+    return launch_stream<FMT_Q4_0>(q, x, y, rows, n_blocks * Q4_0_BLK_BYTES, n_blocks / 2, status, stream, tune, sm_count, info);
 }
 
 }  // namespace axc

@@ -8,7 +8,7 @@
 //  * q4k_matvec_segmented_kernel -- rows longer than 128 superblocks (K > 32768): the row is
 //    cut into K segments of 64 superblocks, each staged through shared memory with one bulk
 //    async copy per row, and y is accumulated over the segments.  Same arithmetic as the
-//    streaming kernel in q4k_stream.cu (which serves every shorter row and explains it).
+//    streaming kernel in q4_stream.cu (which serves every shorter row and explains it).
 //  * q4k_matvec_seq_kernel -- one thread per row in the reference's exact operation order
 //    (separately rounded multiplies and adds); its y is bit-identical to the CPU reference.
 //  * q4k_dequant_kernel -- writes the dequantised weights, bit-identical to the reference's
