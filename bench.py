@@ -55,9 +55,9 @@ def measured_peak():
         return FALLBACK_HBM_GBS, "fallback (6.65 TB/s, earlier measurement on this pool)"
 
 
-# DRAM traffic of one q4k_matvec_stream_kernel launch from an ncu capture of this workload
+# DRAM traffic of one streaming-kernel launch from an ncu capture of this workload
 # (dram__bytes_read.sum + dram__bytes_write.sum); see profiles/.  None until captured.
-NCU_TRAFFIC_BYTES_PER_LAUNCH = None
+NCU_TRAFFIC_BYTES_PER_LAUNCH = 33078784   # ncu: dram__bytes_read.sum 33 078 784 B + dram__bytes_write.sum 0 B (y stays in L2)
 
 
 class ClockSampler:
@@ -318,7 +318,7 @@ def run_ours(args):
     achieved = bytes_per_call_local / (us_per_call * 1e-6) / 1e9   # per GPU
     roofline = {"bound": "hbm", "achieved": round(achieved, 2), "peak": peak, "unit": "GB/s",
                 "frac": round(achieved / peak, 4), "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH,
-                "kernel": "q4k_matvec_stream_kernel", "algorithmic_bytes_per_launch": bytes_per_call_local,
+                "kernel": "q4_matvec_stream_kernel<Q4_K_M>", "algorithmic_bytes_per_launch": bytes_per_call_local,
                 "peak_source": peak_src,
                 "note": "achieved = algorithmic bytes per launch / mean launch-to-launch time over "
                         "the timed region (includes inter-kernel gaps"
