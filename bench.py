@@ -190,7 +190,8 @@ def run_ours(args):
     dev = torch.device("cuda", local_rank)
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
-        dist.init_process_group("nccl", device_id=dev)
+        import datetime
+        dist.init_process_group("nccl", device_id=dev, timeout=datetime.timedelta(seconds=180))
 
     pkg = importlib.import_module("axiom-compute_b200")
     ops = importlib.import_module("axiom-compute_b200.ops")
@@ -253,7 +254,7 @@ def run_ours(args):
     graph = None
     if not args.no_graph:
         graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(graph):
+        with torch.cuda.graph(graph, capture_error_mode="thread_local"):
             step()
 
     def run_step():
@@ -281,18 +282,19 @@ def run_ours(args):
     ev1.record()
     barrier()
     elapsed_ms = ev0.elapsed_time(ev1)
-    # keep the GPU under the same load a little longer so the clock sampler sees it
-    t_end = time.perf_counter() + 0.4
-    while time.perf_counter() < t_end:
-        for _ in range(50):
-            run_step()
-        torch.cuda.synchronize()
-    sampler.stop()
-
     t = torch.tensor([elapsed_ms], dtype=torch.float64, device=dev)
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     elapsed_ms = float(t.item())
+    # Keep the GPU under the same load a little longer so the clock sampler sees it.  The number
+    # of extra steps is derived from the rank-agreed time, so every rank runs the same count
+    # (the steps contain collectives).
+    hold_steps = max(20, min(5000, int(400.0 / max(elapsed_ms / args.steps, 1e-3))))
+    for _ in range(hold_steps):
+        run_step()
+    torch.cuda.synchronize()
+    sampler.stop()
+
     calls = args.steps * N_MATRICES
     bytes_per_call_local = rows_local * row_bytes + K_COLS * 4 + rows_local * 4
     total_bytes = float(calls) * bytes_per_call_local * world
