@@ -104,6 +104,7 @@ SYMBOLS = {
     "axc_cuda_q4_0_dequant": (C.c_int, [_VP, _VP, C.c_uint32, C.c_uint32, _VP]),
     "axc_cuda_q4k_matvec_plan": (C.c_int, [C.c_uint32, C.c_uint32, C.POINTER(AxcTuning), C.c_int32,
                                            C.POINTER(C.c_int32)]),
+    "axc_cuda_q4k_matvec_static": (C.c_int, [_VP, _VP, _VP, C.c_uint32, C.c_uint32, _VP]),
     "axc_cuda_version": (C.c_int, []),
 }
 

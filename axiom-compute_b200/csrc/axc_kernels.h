@@ -16,6 +16,7 @@ struct MatvecTuning {
     int pdl = -1;         // programmatic dependent launch: 0 off, 1 on, 2 on + weights before the wait (-1 = default)
     int resident = 0;     // CTAs per SM the shared-memory budget is cut for (0 = default)
     int dry_run = 0;      // compute the launch geometry only, launch nothing
+    const void* x_prepared = nullptr;  // activations already quantised by launch_q4_quantize_x
 };
 
 struct LaunchInfo {
@@ -35,6 +36,11 @@ cudaError_t launch_q4k_matvec_seq(const uint8_t* q, const float* x, float* y, ui
 // w[r][i] = bit-exact dequantised weight i of row r (x-index order).
 cudaError_t launch_q4k_dequant(const uint8_t* q, float* w, uint32_t rows, uint32_t n_sb,
                                cudaStream_t stream);
+
+// Quantised form of x for `n_pos` 64-column positions (see q4_stream.cu): bytes needed and the
+// kernel that fills them; a matvec launched with tuning.x_prepared set reads it instead of x.
+size_t q4_prepared_x_bytes(uint32_t n_pos);
+cudaError_t launch_q4_quantize_x(const float* x, void* out, uint32_t n_pos, cudaStream_t stream);
 
 cudaError_t launch_q4_0_matvec(const uint8_t* q, const float* x, float* y, uint32_t rows,
                                uint32_t n_blocks, uint32_t* status, cudaStream_t stream,

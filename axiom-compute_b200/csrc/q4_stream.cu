@@ -54,6 +54,7 @@ constexpr int FMT_Q4K = 0, FMT_Q4_0 = 1;
 struct StreamParams {
     const uint8_t* q;
     const float* x;
+    const void* x_prepared;  // digit words + metadata made by q4_quantize_x_kernel (PREPARED kernels)
     float* y;
     uint32_t* status;
     uint32_t rows;
@@ -229,7 +230,58 @@ __device__ __forceinline__ float warp_reduce_transposed(const float (&v)[PASSES]
     return r;
 }
 
-template <int FMT, int PASSES>
+// Quantise the activations of `n_pos` 64-column positions into digit words.  Four threads share
+// a position: thread (pos, qt) loads columns 16qt..16qt+15 (coalesced across the warp), i.e. the
+// four nibble words k = 4qt..4qt+3, so each float4 is one dp4a operand set.  Stored as
+// xs[k][pos] with an XOR swizzle so that these stores and the per-thread reads of the matvec
+// are free of shared-memory bank conflicts; xm[pos] = (sum of columns 0..31, sum of columns
+// 32..63, two factors of 2^(e-21)).  `nthreads` is a multiple of 32; all threads must call.
+__device__ __forceinline__ void quantize_x_positions(const float* __restrict__ x, uint4* xs, float4* xm,
+                                                     uint32_t n_pos, uint32_t pos_end, uint32_t pitch,
+                                                     uint32_t tid, uint32_t nthreads) {
+    {
+        const float4* xg = reinterpret_cast<const float4*>(x);
+        constexpr uint32_t FULL = 0xFFFFFFFFu;
+        const uint32_t qt = tid & 3u;
+        for (uint32_t pos = tid >> 2; pos < pos_end; pos += nthreads >> 2) {
+            const bool valid = pos < n_pos;
+            float4 v[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u)
+                v[u] = valid ? __ldg(xg + pos * 16 + qt * 4 + u) : make_float4(0.f, 0.f, 0.f, 0.f);
+            // largest finite |x| of the chunk (NaNs are ignored by fmaxf) and the half sums
+            float m = 0.0f, s = 0.0f;
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                m = fmaxf(m, fmaxf(fmaxf(fabsf(v[u].x), fabsf(v[u].y)), fmaxf(fabsf(v[u].z), fabsf(v[u].w))));
+                s += (v[u].x + v[u].y) + (v[u].z + v[u].w);
+            }
+            m = fmaxf(m, __shfl_xor_sync(FULL, m, 1));
+            m = fmaxf(m, __shfl_xor_sync(FULL, m, 2));
+            s += __shfl_xor_sync(FULL, s, 1);                     // sum of this 32-column half
+            const float s_other = __shfl_xor_sync(FULL, s, 2);   // sum of the other half
+            m = fminf(m, __int_as_float(0x7F7FFFFF));  // an infinite x makes the row non-finite anyway
+            int e = (int)((__float_as_uint(m) >> 23) & 0xFFu) - 127;
+            if (e < -126) e = -126;
+            const int up = X_FRAC_BITS - e;  // [-106, 147]: two representable power-of-two steps
+            const int up1 = up >> 1;
+            const float f1 = exp2i(up1), f2 = exp2i(up - up1);
+            if (valid) {
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                    const uint32_t k = qt * 4 + u;
+                    xs[k * pitch + (pos ^ (k & 7u))] = quantize_x4(v[u], f1, f2);
+                }
+                if (qt == 0) {
+                    const int dn = -up, dn1 = dn >> 1;  // e - 21 in [-147, 106]
+                    xm[pos] = make_float4(s, s_other, exp2i(dn1), exp2i(dn - dn1));
+                }
+            }
+        }
+    }
+}
+
+template <int FMT, int PASSES, bool PREPARED>
 __global__ void __launch_bounds__(512, 1) q4_matvec_stream_kernel(const StreamParams p) {
     extern __shared__ __align__(128) uint8_t smem[];
     const uint32_t tid = threadIdx.x;
@@ -308,51 +360,13 @@ __global__ void __launch_bounds__(512, 1) q4_matvec_stream_kernel(const StreamPa
     asm volatile("griddepcontrol.wait;" ::: "memory");
     TRACE(1);
 
-    // Quantise x once per CTA.  Four threads share a 64-column chunk position: thread (pos, qt)
-    // loads columns 16qt..16qt+15 (coalesced across the warp), i.e. the four nibble words
-    // k = 4qt..4qt+3 of that half (qt < 2: low nibbles, qt >= 2: high nibbles), so each float4 is
-    // one dp4a operand set.  Stored as xs[k][pos] with an XOR swizzle so that these stores and the
-    // per-thread reads below are free of bank conflicts.
-    {
-        const float4* xg = reinterpret_cast<const float4*>(p.x);
-        constexpr uint32_t FULL = 0xFFFFFFFFu;
-        const uint32_t n_pos = p.n_pos;
-        const uint32_t qt = tid & 3u;
-        for (uint32_t pos = tid >> 2; pos < p.x_pos_end; pos += blockDim.x >> 2) {
-            const bool valid = pos < n_pos;
-            float4 v[4];
-#pragma unroll
-            for (int u = 0; u < 4; ++u)
-                v[u] = valid ? __ldg(xg + pos * 16 + qt * 4 + u) : make_float4(0.f, 0.f, 0.f, 0.f);
-            // largest finite |x| of the chunk (NaNs are ignored by fmaxf) and the half sums
-            float m = 0.0f, s = 0.0f;
-#pragma unroll
-            for (int u = 0; u < 4; ++u) {
-                m = fmaxf(m, fmaxf(fmaxf(fabsf(v[u].x), fabsf(v[u].y)), fmaxf(fabsf(v[u].z), fabsf(v[u].w))));
-                s += (v[u].x + v[u].y) + (v[u].z + v[u].w);
-            }
-            m = fmaxf(m, __shfl_xor_sync(FULL, m, 1));
-            m = fmaxf(m, __shfl_xor_sync(FULL, m, 2));
-            s += __shfl_xor_sync(FULL, s, 1);                     // sum of this 32-column half
-            const float s_other = __shfl_xor_sync(FULL, s, 2);   // sum of the other half
-            m = fminf(m, __int_as_float(0x7F7FFFFF));  // an infinite x makes the row non-finite anyway
-            int e = (int)((__float_as_uint(m) >> 23) & 0xFFu) - 127;
-            if (e < -126) e = -126;
-            const int up = X_FRAC_BITS - e;  // [-106, 147]: two representable power-of-two steps
-            const int up1 = up >> 1;
-            const float f1 = exp2i(up1), f2 = exp2i(up - up1);
-            if (valid) {
-#pragma unroll
-                for (int u = 0; u < 4; ++u) {
-                    const uint32_t k = qt * 4 + u;
-                    xs[k * p.x_pitch + (pos ^ (k & 7u))] = quantize_x4(v[u], f1, f2);
-                }
-                if (qt == 0) {
-                    const int dn = -up, dn1 = dn >> 1;  // e - 21 in [-147, 106]
-                    xm[pos] = make_float4(s, s_other, exp2i(dn1), exp2i(dn - dn1));
-                }
-            }
-        }
+    if constexpr (PREPARED) {
+        // The digit words were produced once by q4_quantize_x_kernel: copy them (and the
+        // per-position sums and scales that follow them) as they are.
+        const uint4* src = reinterpret_cast<const uint4*>(p.x_prepared);
+        for (uint32_t i = tid; i < 17u * p.x_pitch; i += blockDim.x) xs[i] = __ldg(src + i);
+    } else {
+        quantize_x_positions(p.x, xs, xm, p.n_pos, p.x_pos_end, p.x_pitch, tid, blockDim.x);
     }
     if (!p.prefetch_first) start_stream();
     __syncthreads();
@@ -456,6 +470,7 @@ static cudaError_t launch_stream(const uint8_t* q, const float* x, float* y, uin
                                  LaunchInfo* info) {
     StreamParams p{};
     p.q = q, p.x = x, p.y = y, p.status = status, p.rows = rows;
+    p.x_prepared = tune.x_prepared;
     p.row_bytes = row_bytes, p.n_pos = n_pos;
     p.warps_per_row = (n_pos + 31) / 32;
     // CTA shape: whole rows per pass, about `threads` threads.  `ctas_per_sm` sizes the grid,
@@ -535,10 +550,18 @@ static cudaError_t launch_stream(const uint8_t* q, const float* x, float* y, uin
     p.prefetch_first = tune.pdl == 2 || tune.pdl < 0 ? 1u : 0u;
 
     void (*kern)(StreamParams) = nullptr;
-    switch (passes) {
-        case 1: kern = q4_matvec_stream_kernel<FMT, 1>; break;
-        case 2: kern = q4_matvec_stream_kernel<FMT, 2>; break;
-        default: kern = q4_matvec_stream_kernel<FMT, 4>; break;
+    if (tune.x_prepared) {
+        switch (passes) {
+            case 1: kern = q4_matvec_stream_kernel<FMT, 1, true>; break;
+            case 2: kern = q4_matvec_stream_kernel<FMT, 2, true>; break;
+            default: kern = q4_matvec_stream_kernel<FMT, 4, true>; break;
+        }
+    } else {
+        switch (passes) {
+            case 1: kern = q4_matvec_stream_kernel<FMT, 1, false>; break;
+            case 2: kern = q4_matvec_stream_kernel<FMT, 2, false>; break;
+            default: kern = q4_matvec_stream_kernel<FMT, 4, false>; break;
+        }
     }
     if (info) {
         info->grid = (int)grid, info->block = warps * 32, info->smem = smem;
@@ -558,6 +581,25 @@ static cudaError_t launch_stream(const uint8_t* q, const float* x, float* y, uin
     cfg.attrs = attr;
     cfg.numAttrs = tune.pdl != 0 ? 1 : 0;
     return cudaLaunchKernelEx(&cfg, kern, p);
+}
+
+// Stand-alone quantiser: writes what the matvec kernel otherwise builds in shared memory
+// (uint4 digit words [16][pitch] followed by float4 metadata [pitch]) to global memory, once,
+// for callers that feed the same x to several matrices or keep the scratch themselves.
+__global__ void q4_quantize_x_kernel(const float* __restrict__ x, uint4* __restrict__ out, uint32_t n_pos,
+                                     uint32_t pitch) {
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    quantize_x_positions(x, out, reinterpret_cast<float4*>(out + 16 * pitch), n_pos, pitch, pitch,
+                         threadIdx.x, blockDim.x);
+}
+
+size_t q4_prepared_x_bytes(uint32_t n_pos) { return (size_t)17 * ((n_pos + 7) & ~7u) * 16; }
+
+cudaError_t launch_q4_quantize_x(const float* x, void* out, uint32_t n_pos, cudaStream_t stream) {
+    if (n_pos == 0) return cudaSuccess;
+    const uint32_t pitch = (n_pos + 7) & ~7u;
+    q4_quantize_x_kernel<<<1, 512, 0, stream>>>(x, reinterpret_cast<uint4*>(out), n_pos, pitch);
+    return cudaGetLastError();
 }
 
 cudaError_t launch_q4k_matvec_segmented(const uint8_t* q, const float* x, float* y, uint32_t rows,

@@ -227,6 +227,24 @@ int axc_cuda_q4_0_dequant(const void* q, float* w, uint32_t rows, uint32_t n_blo
 int axc_cuda_q4k_matvec_plan(uint32_t rows, uint32_t n_superblocks, const axc_tuning* tuning,
                              int32_t sm_count, int32_t out_grid_block_smem_tile_stages[5]);
 
+/* Q4_K_M matvec that allocates nothing.  It has no counterpart in the reference; it exists for
+ * callers that may not create device memory when they need a matvec: a plug-in inside a host
+ * program that owns the GPU's memory pool and bans driver allocations after start-up, or a
+ * latency-critical decode thread that must avoid cudaMalloc / cudaFree because they synchronise
+ * the device.  q, x, y are the caller's 16-byte aligned device pointers as for
+ * axc_cuda_q4k_matvec; the quantised form of x that the kernel consumes is kept in a fixed
+ * 139 520-byte array inside the library (held by every GPU that loads the library until the
+ * process exits).  Limit: n_superblocks <= AXC_STATIC_MAX_SUPERBLOCKS (K <= 32768); longer rows
+ * return AXC_ERR_BUFFER_ALLOCATION_FAILED, nothing is launched.  The first call on each device
+ * looks up the array's device address (cudaGetSymbolAddress) and should therefore be made with
+ * that device current and before any stream capture begins.  All calls on a device share the
+ * one array: calls whose kernels could overlap on the GPU (different streams) race on it and
+ * must be ordered by the caller; calls in one stream are safe, each call rewrites every word it
+ * later reads.  No cudaMalloc, cudaFree or allocating library routine is called. */
+#define AXC_STATIC_MAX_SUPERBLOCKS 128
+int axc_cuda_q4k_matvec_static(const void* q, const float* x, float* y, uint32_t rows,
+                               uint32_t n_superblocks, void* stream);
+
 /* Library version: major * 10000 + minor * 100 + patch. */
 int axc_cuda_version(void);
 
