@@ -195,6 +195,7 @@ def run_ours(args):
 
     pkg = importlib.import_module("axiom-compute_b200")
     ops = importlib.import_module("axiom-compute_b200.ops")
+    sharding = importlib.import_module("axiom-compute_b200.sharding")
     synth = pkg.synth
 
     strong = args.scaling == "strong" and world > 1
@@ -227,7 +228,7 @@ def run_ours(args):
         for m in range(N_MATRICES):
             ops.q4k_matvec(weights[m], x_dev, rows_local, N_SB, y=y_local[m], status=status)
             if world > 1:
-                dist.all_gather_into_tensor(y_full[m], y_local[m])
+                sharding.all_gather_rows(y_local[m], rows_global, out=y_full[m])
 
     # ---- parity spot check against the oracle before timing (checker only) ----
     step()
