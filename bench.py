@@ -224,9 +224,11 @@ def run_ours(args):
         if world > 1 else None
     status = ops.new_status(dev)
 
+    tuning = ops.make_tuning(pdl=args.pdl) if args.pdl >= 0 else None
+
     def step():
         for m in range(N_MATRICES):
-            ops.q4k_matvec(weights[m], x_dev, rows_local, N_SB, y=y_local[m], status=status)
+            ops.q4k_matvec(weights[m], x_dev, rows_local, N_SB, y=y_local[m], status=status, tuning=tuning)
             if world > 1:
                 sharding.all_gather_rows(y_local[m], rows_global, out=y_full[m])
 
@@ -253,7 +255,10 @@ def run_ours(args):
     torch.cuda.current_stream().wait_stream(side)
     torch.cuda.synchronize()
     graph = None
-    if not args.no_graph:
+    # With collectives in the step the default is plain stream launches: capturing the NCCL
+    # all-gather together with programmatic-dependent-launch kernels hung on this stack.
+    use_graph = not args.no_graph and (world == 1 or args.force_graph)
+    if use_graph:
         graph = torch.cuda.CUDAGraph()
         with torch.cuda.graph(graph, capture_error_mode="thread_local"):
             step()
@@ -418,6 +423,8 @@ def main():
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--scaling", choices=["weak", "strong"], default="weak")
     ap.add_argument("--no-graph", action="store_true", help="launch from the stream, no CUDA graph")
+    ap.add_argument("--force-graph", action="store_true", help="CUDA graph even with collectives in the step")
+    ap.add_argument("--pdl", type=int, default=-1, help="programmatic dependent launch mode (0 off, 1, 2; -1 default)")
     ap.add_argument("--skip-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--skip-e2e", action="store_true", help="skip the host-buffer leg (profiling)")
     args = ap.parse_args()
