@@ -69,6 +69,7 @@ struct StreamParams {
     uint32_t part_entries;   // capacity of the partial-sum array (>= rows per CTA * warps_per_row)
     uint32_t evict_first;
     uint32_t prefetch_first; // start the weight stream before griddepcontrol.wait
+    uint32_t independent;    // x and y are untouched by the previous launch: wait only before writing y
     uint32_t x_pitch;        // positions rounded up to 8
     uint32_t xs_offset;      // byte offset of the digit words  uint4[16][x_pitch]
     uint32_t xm_offset;      // byte offset of the position metadata float4[x_pitch]
@@ -357,7 +358,9 @@ __global__ void __launch_bounds__(512, 1) q4_matvec_stream_kernel(const StreamPa
     if (p.prefetch_first) start_stream();
 
     // x may be the output of the previous kernel in the stream; y may still be read by it.
-    asm volatile("griddepcontrol.wait;" ::: "memory");
+    // A caller that knows neither is the case (say the up projection launched right after the
+    // gate projection of the same x) lets the whole prologue overlap the previous kernel.
+    if (!p.independent) asm volatile("griddepcontrol.wait;" ::: "memory");
     TRACE(1);
 
     if constexpr (PREPARED) {
@@ -453,6 +456,7 @@ __global__ void __launch_bounds__(512, 1) q4_matvec_stream_kernel(const StreamPa
 
     TRACE(18);
     __syncthreads();
+    if (p.independent) asm volatile("griddepcontrol.wait;" ::: "memory");  // stream order for y
     TRACE(19);
     for (uint32_t r = tid; r < my_rows; r += blockDim.x) {
         float sum = part[r * wpr];
@@ -547,7 +551,8 @@ static cudaError_t launch_stream(const uint8_t* q, const float* x, float* y, uin
     p.tiles_lo = (p.rows_base + p.tile_rows - 1) / p.tile_rows;
     p.tiles_hi = (p.rows_base + 1 + p.tile_rows - 1) / p.tile_rows;
     p.evict_first = tune.evict_first > 0 ? 1u : 0u;
-    p.prefetch_first = tune.pdl == 2 || tune.pdl < 0 ? 1u : 0u;
+    p.prefetch_first = tune.pdl >= 2 || tune.pdl < 0 ? 1u : 0u;
+    p.independent = tune.pdl == 3 ? 1u : 0u;
 
     void (*kern)(StreamParams) = nullptr;
     if (tune.x_prepared) {

@@ -224,11 +224,18 @@ def run_ours(args):
         if world > 1 else None
     status = ops.new_status(dev)
 
-    tuning = ops.make_tuning(pdl=args.pdl) if args.pdl >= 0 else None
+    # The 16 calls of a step read the same x and write 16 different y: no call depends on the
+    # one before it, which the caller states with pdl = 3 (only the final store of y waits for
+    # the previous launch).  The strict figure (pdl = 2: x is read only after the previous
+    # launch has completed, as a dependent decode chain needs) is measured beside it.
+    pdl_mode = args.pdl if args.pdl >= 0 else 3
+    tuning = ops.make_tuning(pdl=pdl_mode)
+    tuning_strict = ops.make_tuning(pdl=2)
 
-    def step():
+    def step(tn=None):
+        tn = tuning if tn is None else tn
         for m in range(N_MATRICES):
-            ops.q4k_matvec(weights[m], x_dev, rows_local, N_SB, y=y_local[m], status=status, tuning=tuning)
+            ops.q4k_matvec(weights[m], x_dev, rows_local, N_SB, y=y_local[m], status=status, tuning=tn)
             if world > 1:
                 sharding.all_gather_rows(y_local[m], rows_global, out=y_full[m])
 
@@ -301,6 +308,27 @@ def run_ours(args):
     torch.cuda.synchronize()
     sampler.stop()
 
+    strict = None
+    if world == 1 and graph is not None and pdl_mode == 3:
+        g2 = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g2):
+            step(tuning_strict)
+        for _ in range(5):
+            g2.replay()
+        torch.cuda.synchronize()
+        n2 = max(50, args.steps // 4)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(n2):
+            g2.replay()
+        e1.record()
+        torch.cuda.synchronize()
+        us2 = e0.elapsed_time(e1) * 1e3 / (n2 * N_MATRICES)
+        strict = {"us_per_call": round(us2, 4),
+                  "value": round((rows_local * row_bytes + K_COLS * 4 + rows_local * 4) / us2 / 1e3, 2),
+                  "unit": UNIT, "steps": n2,
+                  "note": "same step with every call ordered after the previous one (pdl = 2)"}
+
     calls = args.steps * N_MATRICES
     bytes_per_call_local = rows_local * row_bytes + K_COLS * 4 + rows_local * 4
     total_bytes = float(calls) * bytes_per_call_local * world
@@ -353,11 +381,14 @@ def run_ours(args):
             "l2": f"inputs larger than L2: {N_MATRICES} distinct weight matrices per GPU "
                   f"({N_MATRICES * rows_local * row_bytes / 1e6:.0f} MB) visited round-robin",
             "launch": "cuda_graph" if graph is not None else "stream",
+            "launch_dependency": {3: "independent calls (shared x, distinct y): pdl=3", 2: "strict stream order: pdl=2",
+                                  1: "strict stream order: pdl=1", 0: "no programmatic dependent launch"}[pdl_mode],
             "parallelism": "single GPU" if world == 1 else
                            f"rows sharded over {world} GPUs + NCCL all-gather of y per call",
         },
         "us_per_call": round(us_per_call, 4),
         "pct_of_8TBs": round(100.0 * (bytes_per_call_local / (us_per_call * 1e-6)) / 8e12, 2),
+        "strict_stream_order": strict,
         "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e,
         "gpu_launches": calls, "clocks": sampler.summary(),
     }

@@ -201,7 +201,10 @@ typedef struct axc_tuning {
     int32_t threads;
     int32_t evict_first; /* -1 = default */
     int32_t pdl;         /* programmatic dependent launch: 0 off, 1 on, 2 on with the weight
-                            stream started before the dependency wait */
+                            stream started before the dependency wait (default), 3 = as 2 and the
+                            caller asserts that x is not written and y neither read nor written
+                            by the previous launch on this stream: only the final store of y
+                            waits for that launch */
     int32_t resident;    /* CTAs per SM the shared-memory budget is cut for; 0 = default */
 } axc_tuning;
 

@@ -183,8 +183,11 @@ def test_q4k_tuning_variants_agree(ops, synth):
     y_ref = oracle.matvec_rows("q4k", q, x, rows, n_sb)
     _y64, mag = oracle.matvec_rows_f64("q4k", q, x, rows, n_sb)
     for kw in (dict(ctas_per_sm=1), dict(ctas_per_sm=2, tile_rows=4, stages=2), dict(tile_rows=16),
-               dict(stages=1), dict(evict_first=1), dict(ctas_per_sm=1, tile_rows=32, stages=3)):
-        y = ops.q4k_matvec(dev(q), dev(x), rows, n_sb, tuning=ops.make_tuning(**kw)).cpu().numpy()
+               dict(stages=1), dict(evict_first=1), dict(ctas_per_sm=1, tile_rows=32, stages=3), dict(pdl=3),
+               dict(pdl=0), dict(threads=512, ctas_per_sm=1), dict(threads=128, ctas_per_sm=4)):
+        for _ in range(2):   # back to back: exercises the programmatic-dependent-launch modes
+            y_d = ops.q4k_matvec(dev(q), dev(x), rows, n_sb, tuning=ops.make_tuning(**kw))
+        y = y_d.cpu().numpy()
         assert (np.abs(y - y_ref) / mag).max() <= NORMWISE_TOL, kw
 
 
