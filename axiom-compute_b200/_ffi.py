@@ -60,6 +60,13 @@ class AxcTuning(C.Structure):
                 ("threads", C.c_int32), ("evict_first", C.c_int32), ("pdl", C.c_int32), ("resident", C.c_int32)]
 
 
+class AxcGather(C.Structure):
+    _fields_ = [("y_peer_bases", C.c_void_p), ("flag_peer_bases", C.c_void_p),
+                ("y_offset_bytes", C.c_uint64), ("flag_offset_bytes", C.c_uint64),
+                ("local_words", C.c_void_p), ("world", C.c_uint32), ("rank", C.c_uint32),
+                ("row_offset", C.c_uint32)]
+
+
 # Every symbol include/axc_cuda.h declares: name -> (restype, argtypes)
 _VP = C.c_void_p
 _U32P = C.POINTER(C.c_uint32)
@@ -104,6 +111,8 @@ SYMBOLS = {
     "axc_cuda_q4_0_dequant": (C.c_int, [_VP, _VP, C.c_uint32, C.c_uint32, _VP]),
     "axc_cuda_q4k_matvec_plan": (C.c_int, [C.c_uint32, C.c_uint32, C.POINTER(AxcTuning), C.c_int32,
                                            C.POINTER(C.c_int32)]),
+    "axc_cuda_q4k_matvec_allgather": (C.c_int, [_VP, _VP, C.c_uint32, C.c_uint32, C.POINTER(AxcGather), _VP, _VP,
+                                                C.POINTER(AxcTuning)]),
     "axc_cuda_q4k_matvec_static": (C.c_int, [_VP, _VP, _VP, C.c_uint32, C.c_uint32, _VP]),
     "axc_cuda_version": (C.c_int, []),
 }

@@ -6,6 +6,15 @@
 
 namespace axc {
 
+// Fused all-gather epilogue of the streaming matvec (one process per GPU, peer-mapped memory).
+struct GatherArgs {
+    const uint64_t* y_peer_bases;     // device array [world]: base address of each rank's y storage
+    const uint64_t* flag_peer_bases;  // device array [world]: base address of each rank's flag words
+    uint64_t y_offset_bytes, flag_offset_bytes;
+    uint32_t* local_words;            // this rank's [0] CTA counter, [1] epoch; zero before first use
+    uint32_t world, rank, row_offset;
+};
+
 // Tunables of the streaming matvec kernels.  0 = let the launcher choose.
 struct MatvecTuning {
     int ctas_per_sm = 0;  // resident CTAs per SM the grid is sized for
@@ -17,6 +26,7 @@ struct MatvecTuning {
     int resident = 0;     // CTAs per SM the shared-memory budget is cut for (0 = default)
     int dry_run = 0;      // compute the launch geometry only, launch nothing
     const void* x_prepared = nullptr;  // activations already quantised by launch_q4_quantize_x
+    const GatherArgs* gather = nullptr;  // all-gather fused into the epilogue (y is ignored)
 };
 
 struct LaunchInfo {

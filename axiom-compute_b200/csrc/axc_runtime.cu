@@ -757,6 +757,26 @@ int axc_cuda_q4_0_dequant(const void* q, float* w, uint32_t rows, uint32_t n_blo
     return launch_result(axc::launch_q4_0_dequant((const uint8_t*)q, w, rows, n_blocks, (cudaStream_t)stream));
 }
 
+int axc_cuda_q4k_matvec_allgather(const void* q, const float* x, uint32_t rows_local,
+                                  uint32_t n_superblocks, const axc_gather* g, void* stream,
+                                  uint32_t* status, const axc_tuning* tuning) {
+    clear_error();
+    if (rows_local == 0) return AXC_OK;
+    if (!g || !g->y_peer_bases || !g->flag_peer_bases || !g->local_words || g->world == 0 || g->rank >= g->world)
+        return fail(AXC_ERR_INVALID_ARGUMENT, "incomplete all-gather description");
+    if (!q || !x || (((uintptr_t)q | (uintptr_t)x) & 15u))
+        return fail(AXC_ERR_INVALID_ARGUMENT, "q and x must be non-null and 16-byte aligned");
+    if (n_superblocks == 0 || n_superblocks > 128)
+        return fail(AXC_ERR_INVALID_ARGUMENT, "the fused all-gather serves rows of 1..128 superblocks");
+    axc::GatherArgs ga{};
+    ga.y_peer_bases = g->y_peer_bases, ga.flag_peer_bases = g->flag_peer_bases;
+    ga.y_offset_bytes = g->y_offset_bytes, ga.flag_offset_bytes = g->flag_offset_bytes;
+    ga.local_words = g->local_words, ga.world = g->world, ga.rank = g->rank, ga.row_offset = g->row_offset;
+    axc::MatvecTuning t = to_tuning(tuning);
+    t.gather = &ga;
+    return launch_result(axc::launch_q4k_matvec((const uint8_t*)q, x, nullptr, rows_local, n_superblocks, status, (cudaStream_t)stream, t, sm_count_of_current_device(), nullptr));
+}
+
 int axc_cuda_q4k_matvec_plan(uint32_t rows, uint32_t n_superblocks, const axc_tuning* tuning,
                              int32_t sm_count, int32_t out[5]) {
     clear_error();

@@ -77,6 +77,14 @@ struct StreamParams {
     uint32_t rows_rem;       // rows % grid: the first rows_rem CTAs take one row more
     uint32_t tiles_lo, tiles_hi;  // tiles of a CTA with rows_base / rows_base + 1 rows
     uint32_t x_pos_end;      // positions rounded up to a whole warp's worth (8)
+    // fused all-gather epilogue (GATHER kernels): every rank stores its y slice into every rank's
+    // full-length vector through peer mappings, then the ranks exchange one flag each
+    const uint64_t* y_peer_bases;     // device array [world]: base address of each rank's y storage
+    const uint64_t* flag_peer_bases;  // device array [world]: base address of each rank's flag words
+    uint64_t y_offset_bytes;          // offset of this call's vector inside the y storage
+    uint64_t flag_offset_bytes;       // offset of this call's flag row (uint32[world])
+    uint32_t* local_words;            // this rank's own words: [0] CTAs done, [1] epoch of this flag row
+    uint32_t world, rank, row_offset;
 };
 
 __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
@@ -282,7 +290,7 @@ __device__ __forceinline__ void quantize_x_positions(const float* __restrict__ x
     }
 }
 
-template <int FMT, int PASSES, bool PREPARED>
+template <int FMT, int PASSES, bool PREPARED, bool GATHER>
 __global__ void __launch_bounds__(512, 1) q4_matvec_stream_kernel(const StreamParams p) {
     extern __shared__ __align__(128) uint8_t smem[];
     const uint32_t tid = threadIdx.x;
@@ -458,10 +466,50 @@ __global__ void __launch_bounds__(512, 1) q4_matvec_stream_kernel(const StreamPa
     __syncthreads();
     if (p.independent) asm volatile("griddepcontrol.wait;" ::: "memory");  // stream order for y
     TRACE(19);
-    for (uint32_t r = tid; r < my_rows; r += blockDim.x) {
-        float sum = part[r * wpr];
-        for (uint32_t wv = 1; wv < wpr; ++wv) sum += part[r * wpr + wv];
-        p.y[r0 + r] = sum;
+    if constexpr (!GATHER) {
+        for (uint32_t r = tid; r < my_rows; r += blockDim.x) {
+            float sum = part[r * wpr];
+            for (uint32_t wv = 1; wv < wpr; ++wv) sum += part[r * wpr + wv];
+            p.y[r0 + r] = sum;
+        }
+    } else {
+        // All-gather fused into the epilogue: the slice goes straight into every rank's vector
+        // (plain peer stores over NVLink; no multicast, no TMA on peer memory).
+        for (uint32_t r = tid; r < my_rows; r += blockDim.x) {
+            float sum = part[r * wpr];
+            for (uint32_t wv = 1; wv < wpr; ++wv) sum += part[r * wpr + wv];
+            for (uint32_t pr = 0; pr < p.world; ++pr) {
+                float* dst = reinterpret_cast<float*>(p.y_peer_bases[pr] + p.y_offset_bytes);
+                dst[p.row_offset + r0 + r] = sum;
+            }
+        }
+        __threadfence_system();  // this thread's peer stores are visible system-wide
+        __syncthreads();
+        if (tid == 0) {
+            const uint32_t done = atomicAdd(&p.local_words[0], 1u);
+            if (done == gridDim.x - 1) {  // last CTA of this rank: the whole slice is out
+                __threadfence_system();
+                p.local_words[0] = 0;     // ready for the next launch (stream order)
+                const uint32_t epoch = ++p.local_words[1];
+                for (uint32_t pr = 0; pr < p.world; ++pr) {
+                    uint32_t* f = reinterpret_cast<uint32_t*>(p.flag_peer_bases[pr] + p.flag_offset_bytes) + p.rank;
+                    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(f), "r"(epoch) : "memory");
+                }
+                // The kernel ends only when every rank's slice has landed here, so anything later
+                // in this stream may read the assembled vector.  Bounded: a rank that never
+                // arrives costs about two seconds and sets an error bit, it does not hang the GPU.
+                const uint32_t* mine = reinterpret_cast<const uint32_t*>(p.flag_peer_bases[p.rank] + p.flag_offset_bytes);
+                for (uint32_t pr = 0; pr < p.world; ++pr) {
+                    uint32_t seen = 0, it = 0;
+                    for (; it < (1u << 22); ++it) {
+                        asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(mine + pr) : "memory");
+                        if ((int32_t)(seen - epoch) >= 0) break;
+                        __nanosleep(200);
+                    }
+                    if (it == (1u << 22) && p.status) atomicOr(p.status, ERR_PEER_WAIT_TIMEOUT);
+                }
+            }
+        }
     }
 }
 
@@ -555,17 +603,27 @@ static cudaError_t launch_stream(const uint8_t* q, const float* x, float* y, uin
     p.independent = tune.pdl == 3 ? 1u : 0u;
 
     void (*kern)(StreamParams) = nullptr;
-    if (tune.x_prepared) {
+    if (tune.gather) {
+        const GatherArgs& g = *tune.gather;
+        p.y_peer_bases = g.y_peer_bases, p.flag_peer_bases = g.flag_peer_bases;
+        p.y_offset_bytes = g.y_offset_bytes, p.flag_offset_bytes = g.flag_offset_bytes;
+        p.local_words = g.local_words, p.world = g.world, p.rank = g.rank, p.row_offset = g.row_offset;
         switch (passes) {
-            case 1: kern = q4_matvec_stream_kernel<FMT, 1, true>; break;
-            case 2: kern = q4_matvec_stream_kernel<FMT, 2, true>; break;
-            default: kern = q4_matvec_stream_kernel<FMT, 4, true>; break;
+            case 1: kern = q4_matvec_stream_kernel<FMT, 1, false, true>; break;
+            case 2: kern = q4_matvec_stream_kernel<FMT, 2, false, true>; break;
+            default: kern = q4_matvec_stream_kernel<FMT, 4, false, true>; break;
+        }
+    } else if (tune.x_prepared) {
+        switch (passes) {
+            case 1: kern = q4_matvec_stream_kernel<FMT, 1, true, false>; break;
+            case 2: kern = q4_matvec_stream_kernel<FMT, 2, true, false>; break;
+            default: kern = q4_matvec_stream_kernel<FMT, 4, true, false>; break;
         }
     } else {
         switch (passes) {
-            case 1: kern = q4_matvec_stream_kernel<FMT, 1, false>; break;
-            case 2: kern = q4_matvec_stream_kernel<FMT, 2, false>; break;
-            default: kern = q4_matvec_stream_kernel<FMT, 4, false>; break;
+            case 1: kern = q4_matvec_stream_kernel<FMT, 1, false, false>; break;
+            case 2: kern = q4_matvec_stream_kernel<FMT, 2, false, false>; break;
+            default: kern = q4_matvec_stream_kernel<FMT, 4, false, false>; break;
         }
     }
     if (info) {

@@ -219,6 +219,19 @@ def run_ours(args):
         if strong:
             w = w[rank * rows_local * row_bytes:(rank + 1) * rows_local * row_bytes]
         weights.append(torch.from_numpy(np.ascontiguousarray(w)).to(dev))
+    # N > 1: the all-gather is fused into the matvec epilogue (peer stores over NVLink + one flag
+    # per rank); `--collective nccl` keeps the plain NCCL all-gather after each call instead.
+    gather = None
+    collective = "none"
+    if world > 1:
+        collective = args.collective
+        if collective == "fused":
+            try:
+                coll = importlib.import_module("axiom-compute_b200.collective")
+                gather = coll.PeerGather(rows_global, N_MATRICES, dev)
+            except Exception as exc:   # symmetric memory not available on this box
+                sys.stderr.write(f"bench.py: fused all-gather unavailable ({exc!r}); using NCCL\n")
+                collective = "nccl"
     y_local = [torch.empty(rows_local, dtype=torch.float32, device=dev) for _ in range(N_MATRICES)]
     y_full = [torch.empty(rows_global, dtype=torch.float32, device=dev) for _ in range(N_MATRICES)] \
         if world > 1 else None
@@ -235,9 +248,12 @@ def run_ours(args):
     def step(tn=None):
         tn = tuning if tn is None else tn
         for m in range(N_MATRICES):
-            ops.q4k_matvec(weights[m], x_dev, rows_local, N_SB, y=y_local[m], status=status, tuning=tn)
-            if world > 1:
-                sharding.all_gather_rows(y_local[m], rows_global, out=y_full[m])
+            if gather is not None:
+                gather.matvec(weights[m], x_dev, N_SB, m, status=status, tuning=tn)
+            else:
+                ops.q4k_matvec(weights[m], x_dev, rows_local, N_SB, y=y_local[m], status=status, tuning=tn)
+                if world > 1:
+                    sharding.all_gather_rows(y_local[m], rows_global, out=y_full[m])
 
     # ---- parity spot check against the oracle before timing (checker only) ----
     step()
@@ -249,7 +265,8 @@ def run_ours(args):
         rs = 64
         y_ref = oracle.matvec_rows("q4k", weights[0][:rs * row_bytes].cpu().numpy(), x_host, rs, N_SB)
         _y64, mag = oracle.matvec_rows_f64("q4k", weights[0][:rs * row_bytes].cpu().numpy(), x_host, rs, N_SB)
-        err = float((np.abs(y_local[0][:rs].cpu().numpy() - y_ref) / mag).max())
+        got = gather.vector(0)[gather.row_offset:gather.row_offset + rs] if gather is not None else y_local[0][:rs]
+        err = float((np.abs(got.cpu().numpy() - y_ref) / mag).max())
         if not err <= 1e-5:
             raise SystemExit(f"parity check failed before timing: norm-wise error {err:.3e}")
 
@@ -264,7 +281,7 @@ def run_ours(args):
     graph = None
     # With collectives in the step the default is plain stream launches: capturing the NCCL
     # all-gather together with programmatic-dependent-launch kernels hung on this stack.
-    use_graph = not args.no_graph and (world == 1 or args.force_graph)
+    use_graph = not args.no_graph and (world == 1 or gather is not None or args.force_graph)
     if use_graph:
         graph = torch.cuda.CUDAGraph()
         with torch.cuda.graph(graph, capture_error_mode="thread_local"):
@@ -384,7 +401,7 @@ def run_ours(args):
             "launch_dependency": {3: "independent calls (shared x, distinct y): pdl=3", 2: "strict stream order: pdl=2",
                                   1: "strict stream order: pdl=1", 0: "no programmatic dependent launch"}[pdl_mode],
             "parallelism": "single GPU" if world == 1 else
-                           f"rows sharded over {world} GPUs + NCCL all-gather of y per call",
+                           f"rows sharded over {world} GPUs + all-gather of y per call ({collective})",
         },
         "us_per_call": round(us_per_call, 4),
         "pct_of_8TBs": round(100.0 * (bytes_per_call_local / (us_per_call * 1e-6)) / 8e12, 2),
@@ -454,6 +471,8 @@ def main():
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--scaling", choices=["weak", "strong"], default="weak")
     ap.add_argument("--no-graph", action="store_true", help="launch from the stream, no CUDA graph")
+    ap.add_argument("--collective", choices=["fused", "nccl"], default="fused",
+                    help="N > 1: all-gather fused into the matvec epilogue, or NCCL after each call")
     ap.add_argument("--force-graph", action="store_true", help="CUDA graph even with collectives in the step")
     ap.add_argument("--pdl", type=int, default=-1, help="programmatic dependent launch mode (0 off, 1, 2; -1 default)")
     ap.add_argument("--skip-cpu", action="store_true", help="skip the CPU baseline leg")

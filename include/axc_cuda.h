@@ -226,6 +226,32 @@ int axc_cuda_q4k_dequant(const void* q, float* w, uint32_t rows, uint32_t n_supe
                          void* stream);
 int axc_cuda_q4_0_dequant(const void* q, float* w, uint32_t rows, uint32_t n_blocks,
                           void* stream);
+/* Row-sharded matvec with the all-gather of y fused into the kernel (one process per GPU).
+ * The reference has no multi-GPU path; this is the exchange step of sharding its rows over the
+ * GPUs of one node.  Every rank computes `rows_local` rows and stores them at
+ * [row_offset, row_offset + rows_local) of EVERY rank's full-length vector through peer-mapped
+ * memory (plain stores over NVLink), then the ranks exchange one flag each; the kernel returns
+ * only when all slices have arrived in this rank's vector, so later work in the same stream may
+ * read it.  The wait is bounded (about two seconds), after which bit 4 of *status is set.
+ *   y_peer_bases / flag_peer_bases: DEVICE arrays of `world` addresses (this process's mappings
+ *     of each rank's y storage and flag storage; entry `rank` is the local buffer);
+ *   y_offset_bytes: where this call's vector (fp32, global row count) starts in the y storage;
+ *   flag_offset_bytes: where this call's flag row (uint32[world], zero before first use) starts;
+ *   local_words: two uint32 of this rank (zero before first use) tied to that flag row.
+ * All ranks must issue the same sequence of calls per flag row.  Reusing a vector needs one
+ * other all-gather call in between (double buffering). */
+typedef struct axc_gather {
+    const uint64_t* y_peer_bases;
+    const uint64_t* flag_peer_bases;
+    uint64_t y_offset_bytes;
+    uint64_t flag_offset_bytes;
+    uint32_t* local_words;
+    uint32_t world, rank, row_offset;
+} axc_gather;
+int axc_cuda_q4k_matvec_allgather(const void* q, const float* x, uint32_t rows_local,
+                                  uint32_t n_superblocks, const axc_gather* g, void* stream,
+                                  uint32_t* status, const axc_tuning* tuning);
+
 /* Launch geometry the matvec launchers would use (no launch). */
 int axc_cuda_q4k_matvec_plan(uint32_t rows, uint32_t n_superblocks, const axc_tuning* tuning,
                              int32_t sm_count, int32_t out_grid_block_smem_tile_stages[5]);

@@ -209,6 +209,31 @@ def test_q4k_ring_refill_path(ops, synth):
         assert (np.abs(y.cpu().numpy() - y_ref) / mag).max() <= NORMWISE_TOL, kw
 
 
+def test_q4k_fused_allgather_epilogue_single_rank(synth):
+    """The all-gather epilogue with world = 1 (peer table = own buffer): slices land at the row
+    offset of the right slot, flags and epochs advance per call, back-to-back calls are ordered."""
+    from conftest import load_pkg
+    coll = load_pkg("collective")
+    ops_ = load_pkg("ops")
+    rows, n_sb, slots = 777, 16, 3
+    pg = coll.PeerGather(rows, slots, "cuda")
+    assert (pg.world, pg.rank, pg.row_offset, pg.rows_local) == (1, 0, 0, rows)
+    st = ops_.new_status()
+    for it in range(2):
+        for slot in range(slots):
+            q = synth.q4k_weights(rows, n_sb, 4000 + 10 * it + slot)
+            x = synth.activations(n_sb * 256, 4100 + 10 * it + slot)
+            y = pg.matvec(dev(q), dev(x), n_sb, slot, status=st)
+            y_plain = ops_.q4k_matvec(dev(q), dev(x), rows, n_sb)
+            assert torch.equal(y, y_plain)
+            y_ref = oracle.matvec_rows("q4k", q, x, rows, n_sb)
+            _y64, mag = oracle.matvec_rows_f64("q4k", q, x, rows, n_sb)
+            assert (np.abs(y.cpu().numpy() - y_ref) / mag).max() <= NORMWISE_TOL
+    assert int(st.item()) == 0
+    assert pg.flags.cpu().tolist() == [2] * slots                    # epoch 2 published per slot
+    assert pg.local_words.cpu().tolist() == [0, 2] * slots          # CTA counter reset, epoch 2
+
+
 # ---------------------------------------------------------------------------------- Q4_0
 
 @pytest.mark.parametrize("rows,n", [(1, 1), (3, 2), (5, 7), (8, 128), (2, 1024), (2, 1030)])
