@@ -61,10 +61,8 @@ class AxcTuning(C.Structure):
 
 
 class AxcGather(C.Structure):
-    _fields_ = [("y_peer_bases", C.c_void_p), ("flag_peer_bases", C.c_void_p),
-                ("y_offset_bytes", C.c_uint64), ("flag_offset_bytes", C.c_uint64),
-                ("local_words", C.c_void_p), ("world", C.c_uint32), ("rank", C.c_uint32),
-                ("row_offset", C.c_uint32)]
+    _fields_ = [("y_peer_bases", C.c_void_p), ("y_offset_bytes", C.c_uint64), ("epoch", C.c_void_p),
+                ("world", C.c_uint32), ("rank", C.c_uint32), ("row_offset", C.c_uint32)]
 
 
 # Every symbol include/axc_cuda.h declares: name -> (restype, argtypes)
@@ -113,6 +111,8 @@ SYMBOLS = {
                                            C.POINTER(C.c_int32)]),
     "axc_cuda_q4k_matvec_allgather": (C.c_int, [_VP, _VP, C.c_uint32, C.c_uint32, C.POINTER(AxcGather), _VP, _VP,
                                                 C.POINTER(AxcTuning)]),
+    "axc_cuda_gather_next_epoch": (C.c_int, [_VP, _VP]),
+    "axc_cuda_gather_finish": (C.c_int, [_VP, _VP, _VP, C.c_uint32, _VP, _VP]),
     "axc_cuda_q4k_matvec_static": (C.c_int, [_VP, _VP, _VP, C.c_uint32, C.c_uint32, _VP]),
     "axc_cuda_version": (C.c_int, []),
 }

@@ -1,11 +1,13 @@
 """Fused matvec + all-gather over NVLink peer memory (one process per GPU).
 
-``PeerGather`` owns the symmetric buffers: ``slots`` full-length y vectors and one flag row per
-slot on every rank, mapped into every rank's address space by torch's symmetric memory
-(plumbing only; the stores, flags and waits are in the CUDA kernel).  ``matvec`` launches the
-row-sharded Q4_K_M matvec whose epilogue writes this rank's slice into every rank's vector and
-returns the assembled local vector (valid for later work in the same stream).
-With ``world == 1`` it needs no process group and degenerates to a plain matvec into the buffer.
+``PeerGather`` owns the buffers: on every rank ``slots`` full-length vectors of (value, epoch)
+words, mapped into every rank's address space by torch's symmetric memory (plumbing only; the
+stores and the waits are in the CUDA kernels), plus a local fp32 copy and the epoch counter.
+One step is ``begin_step()``, any number of ``matvec()`` calls into distinct slots, ``finish()``:
+``matvec`` launches the row-sharded Q4_K_M matvec whose epilogue stores this rank's slice into
+every rank's vector without waiting for anyone; ``finish`` waits until every word of every slot
+carries the step's epoch and unpacks the values, after which ``vector(slot)`` is complete for
+later work in the same stream.  With ``world == 1`` no process group is needed.
 """
 from __future__ import annotations
 
@@ -24,51 +26,62 @@ class PeerGather:
         self.rows_global, self.slots = int(rows_global), int(slots)
         self.device = torch.device(device)
         self.world, self.rank = 1, 0
-        n_y = self.slots * self.rows_global
+        n = self.slots * self.rows_global
         if group is not None or (torch.distributed.is_available() and torch.distributed.is_initialized()
                                  and torch.distributed.get_world_size() > 1):
             import torch.distributed as dist
             import torch.distributed._symmetric_memory as symm_mem
             group = group if group is not None else dist.group.WORLD
             self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
-            self.y_store = symm_mem.empty(n_y, dtype=torch.float32, device=self.device)
-            self.flags = symm_mem.empty(self.slots * self.world, dtype=torch.int32, device=self.device)
-            self.y_store.zero_()
-            self.flags.zero_()
-            hy = symm_mem.rendezvous(self.y_store, group)
-            hf = symm_mem.rendezvous(self.flags, group)
-            y_ptrs, f_ptrs = list(hy.buffer_ptrs), list(hf.buffer_ptrs)
-            self._handles = (hy, hf)
+            self.pairs = symm_mem.empty(n, dtype=torch.int64, device=self.device)
+            self.pairs.zero_()
+            self._handle = symm_mem.rendezvous(self.pairs, group)
+            ptrs = list(self._handle.buffer_ptrs)
             torch.cuda.synchronize(self.device)
             dist.barrier(group)   # every rank's zeroing is done before anyone stores into it
         else:
-            self.y_store = torch.zeros(n_y, dtype=torch.float32, device=self.device)
-            self.flags = torch.zeros(self.slots, dtype=torch.int32, device=self.device)
-            y_ptrs, f_ptrs = [self.y_store.data_ptr()], [self.flags.data_ptr()]
-        self.y_ptr_table = torch.tensor(y_ptrs, dtype=torch.int64, device=self.device)
-        self.f_ptr_table = torch.tensor(f_ptrs, dtype=torch.int64, device=self.device)
-        self.local_words = torch.zeros(2 * self.slots, dtype=torch.int32, device=self.device)
+            self.pairs = torch.zeros(n, dtype=torch.int64, device=self.device)
+            ptrs = [self.pairs.data_ptr()]
+        self.ptr_table = torch.tensor(ptrs, dtype=torch.int64, device=self.device)
+        self.epoch = torch.zeros(1, dtype=torch.int32, device=self.device)
+        self.values = torch.zeros(n, dtype=torch.float32, device=self.device)
         self.row_offset, self.rows_local = shard_rows(self.rows_global, self.world, self.rank)
 
+    def _stream(self) -> int:
+        return int(torch.cuda.current_stream(self.device).cuda_stream)
+
     def vector(self, slot: int) -> torch.Tensor:
-        """This rank's copy of the assembled vector of `slot`."""
-        return self.y_store[slot * self.rows_global:(slot + 1) * self.rows_global]
+        """This rank's copy of the assembled vector of `slot` (complete after ``finish``)."""
+        return self.values[slot * self.rows_global:(slot + 1) * self.rows_global]
+
+    def begin_step(self) -> None:
+        """Advance the epoch; every rank calls it once before the step's matvec calls."""
+        with torch.cuda.device(self.device):
+            _raise_for(_ffi.lib().axc_cuda_gather_next_epoch(self.epoch.data_ptr(), self._stream()))
 
     def matvec(self, q: torch.Tensor, x: torch.Tensor, n_superblocks: int, slot: int,
-               status: Optional[torch.Tensor] = None, tuning=None) -> torch.Tensor:
-        """y[row_offset : row_offset + rows_local] = this rank's rows; returns the full vector."""
+               status: Optional[torch.Tensor] = None, tuning=None) -> None:
+        """Rows [row_offset, row_offset + rows_local) of `slot`, stored on every rank."""
         if not (q.is_cuda and x.is_cuda):
             raise ValueError("q and x must be CUDA tensors (this backend has no CPU path)")
         if q.numel() < self.rows_local * n_superblocks * 144 or x.numel() < n_superblocks * 256:
             raise ValueError("q or x too small for this rank's shard")
-        g = _ffi.AxcGather(self.y_ptr_table.data_ptr(), self.f_ptr_table.data_ptr(),
-                           slot * self.rows_global * 4, slot * self.world * 4,
-                           self.local_words.data_ptr() + slot * 8, self.world, self.rank, self.row_offset)
+        if not 0 <= slot < self.slots:
+            raise ValueError("slot out of range")
+        g = _ffi.AxcGather(self.ptr_table.data_ptr(), slot * self.rows_global * 8, self.epoch.data_ptr(),
+                           self.world, self.rank, self.row_offset)
         with torch.cuda.device(self.device):
             rc = _ffi.lib().axc_cuda_q4k_matvec_allgather(
-                q.data_ptr(), x.data_ptr(), self.rows_local, n_superblocks, C.byref(g),
-                int(torch.cuda.current_stream().cuda_stream),
+                q.data_ptr(), x.data_ptr(), self.rows_local, n_superblocks, C.byref(g), self._stream(),
                 status.data_ptr() if status is not None else None,
                 C.byref(tuning) if tuning is not None else None)
         _raise_for(rc)
-        return self.vector(slot)
+
+    def finish(self, status: Optional[torch.Tensor] = None, slots: Optional[int] = None) -> None:
+        """Wait for the step's words of the first `slots` slots (default all) and unpack them."""
+        n = (self.slots if slots is None else int(slots)) * self.rows_global
+        with torch.cuda.device(self.device):
+            rc = _ffi.lib().axc_cuda_gather_finish(
+                self.pairs.data_ptr(), self.epoch.data_ptr(), self.values.data_ptr(), n, self._stream(),
+                status.data_ptr() if status is not None else None)
+        _raise_for(rc)

@@ -108,16 +108,7 @@ __device__ __forceinline__ uint64_t l2_evict_first_policy() {
 
 // Packed fp32x2 FMA (two independent fp32 FMAs per instruction on sm_100): acc += a * b.
 __device__ __forceinline__ void ffma2(uint64_t& acc, uint64_t a, uint64_t b) {
-#ifdef AXC_EXP_SCALARFMA
-    float a0, a1, b0, b1, c0, c1;
-    asm("mov.b64 {%0, %1}, %2;" : "=f"(a0), "=f"(a1) : "l"(a));
-    asm("mov.b64 {%0, %1}, %2;" : "=f"(b0), "=f"(b1) : "l"(b));
-    asm("mov.b64 {%0, %1}, %2;" : "=f"(c0), "=f"(c1) : "l"(acc));
-    c0 = fmaf(a0, b0, c0), c1 = fmaf(a1, b1, c1);
-    asm("mov.b64 %0, {%1, %2};" : "=l"(acc) : "f"(c0), "f"(c1));
-#else
     asm("fma.rn.f32x2 %0, %1, %2, %0;" : "+l"(acc) : "l"(a), "l"(b));
-#endif
 }
 
 __device__ __forceinline__ uint64_t pack_f32x2(float lo, float hi) {

@@ -8,10 +8,9 @@ namespace axc {
 
 // Fused all-gather epilogue of the streaming matvec (one process per GPU, peer-mapped memory).
 struct GatherArgs {
-    const uint64_t* y_peer_bases;     // device array [world]: base address of each rank's y storage
-    const uint64_t* flag_peer_bases;  // device array [world]: base address of each rank's flag words
-    uint64_t y_offset_bytes, flag_offset_bytes;
-    uint32_t* local_words;            // this rank's [0] CTA counter, [1] epoch; zero before first use
+    const uint64_t* y_peer_bases;  // device array [world]: base address of each rank's pair storage
+    uint64_t y_offset_bytes;       // this call's vector (8 bytes per global row) inside that storage
+    const uint32_t* epoch_ptr;     // this rank's epoch counter
     uint32_t world, rank, row_offset;
 };
 
@@ -46,6 +45,10 @@ cudaError_t launch_q4k_matvec_seq(const uint8_t* q, const float* x, float* y, ui
 // w[r][i] = bit-exact dequantised weight i of row r (x-index order).
 cudaError_t launch_q4k_dequant(const uint8_t* q, float* w, uint32_t rows, uint32_t n_sb,
                                cudaStream_t stream);
+
+cudaError_t launch_gather_finish(const uint64_t* pairs, const uint32_t* epoch_ptr, float* out, uint32_t n,
+                                 uint32_t* status, cudaStream_t stream);
+cudaError_t launch_gather_next_epoch(uint32_t* epoch_ptr, cudaStream_t stream);
 
 // Quantised form of x for `n_pos` 64-column positions (see q4_stream.cu): bytes needed and the
 // kernel that fills them; a matvec launched with tuning.x_prepared set reads it instead of x.

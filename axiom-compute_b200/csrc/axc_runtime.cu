@@ -762,19 +762,33 @@ int axc_cuda_q4k_matvec_allgather(const void* q, const float* x, uint32_t rows_l
                                   uint32_t* status, const axc_tuning* tuning) {
     clear_error();
     if (rows_local == 0) return AXC_OK;
-    if (!g || !g->y_peer_bases || !g->flag_peer_bases || !g->local_words || g->world == 0 || g->rank >= g->world)
+    if (!g || !g->y_peer_bases || !g->epoch || g->world == 0 || g->world > 16 || g->rank >= g->world || (g->y_offset_bytes & 7u))
         return fail(AXC_ERR_INVALID_ARGUMENT, "incomplete all-gather description");
     if (!q || !x || (((uintptr_t)q | (uintptr_t)x) & 15u))
         return fail(AXC_ERR_INVALID_ARGUMENT, "q and x must be non-null and 16-byte aligned");
     if (n_superblocks == 0 || n_superblocks > 128)
         return fail(AXC_ERR_INVALID_ARGUMENT, "the fused all-gather serves rows of 1..128 superblocks");
     axc::GatherArgs ga{};
-    ga.y_peer_bases = g->y_peer_bases, ga.flag_peer_bases = g->flag_peer_bases;
-    ga.y_offset_bytes = g->y_offset_bytes, ga.flag_offset_bytes = g->flag_offset_bytes;
-    ga.local_words = g->local_words, ga.world = g->world, ga.rank = g->rank, ga.row_offset = g->row_offset;
+    ga.y_peer_bases = g->y_peer_bases, ga.y_offset_bytes = g->y_offset_bytes, ga.epoch_ptr = g->epoch;
+    ga.world = g->world, ga.rank = g->rank, ga.row_offset = g->row_offset;
     axc::MatvecTuning t = to_tuning(tuning);
     t.gather = &ga;
     return launch_result(axc::launch_q4k_matvec((const uint8_t*)q, x, nullptr, rows_local, n_superblocks, status, (cudaStream_t)stream, t, sm_count_of_current_device(), nullptr));
+}
+
+int axc_cuda_gather_next_epoch(uint32_t* epoch, void* stream) {
+    clear_error();
+    if (!epoch) return fail(AXC_ERR_INVALID_ARGUMENT, "null epoch counter");
+    return launch_result(axc::launch_gather_next_epoch(epoch, (cudaStream_t)stream));
+}
+
+int axc_cuda_gather_finish(const uint64_t* pairs, const uint32_t* epoch, float* out, uint32_t n,
+                           void* stream, uint32_t* status) {
+    clear_error();
+    if (n == 0) return AXC_OK;
+    if (!pairs || !epoch || !out || ((uintptr_t)pairs & 7u))
+        return fail(AXC_ERR_INVALID_ARGUMENT, "null or misaligned pair storage / epoch / output");
+    return launch_result(axc::launch_gather_finish(pairs, epoch, out, n, status, (cudaStream_t)stream));
 }
 
 int axc_cuda_q4k_matvec_plan(uint32_t rows, uint32_t n_superblocks, const axc_tuning* tuning,

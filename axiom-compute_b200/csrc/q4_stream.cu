@@ -77,13 +77,11 @@ struct StreamParams {
     uint32_t rows_rem;       // rows % grid: the first rows_rem CTAs take one row more
     uint32_t tiles_lo, tiles_hi;  // tiles of a CTA with rows_base / rows_base + 1 rows
     uint32_t x_pos_end;      // positions rounded up to a whole warp's worth (8)
-    // fused all-gather epilogue (GATHER kernels): every rank stores its y slice into every rank's
-    // full-length vector through peer mappings, then the ranks exchange one flag each
-    const uint64_t* y_peer_bases;     // device array [world]: base address of each rank's y storage
-    const uint64_t* flag_peer_bases;  // device array [world]: base address of each rank's flag words
-    uint64_t y_offset_bytes;          // offset of this call's vector inside the y storage
-    uint64_t flag_offset_bytes;       // offset of this call's flag row (uint32[world])
-    uint32_t* local_words;            // this rank's own words: [0] CTAs done, [1] epoch of this flag row
+    // fused all-gather epilogue (GATHER kernels): every rank stores its y slice, each value
+    // paired with the current epoch in one 8-byte word, into every rank's full-length vector
+    const uint64_t* y_peer_bases;  // device array [world]: base address of each rank's pair storage
+    uint64_t y_offset_bytes;       // offset of this call's vector (uint2[global rows]) in that storage
+    const uint32_t* epoch_ptr;     // this rank's epoch counter (advanced once per step by the caller)
     uint32_t world, rank, row_offset;
 };
 
@@ -370,6 +368,14 @@ __global__ void __launch_bounds__(512, 1) q4_matvec_stream_kernel(const StreamPa
     // gate projection of the same x) lets the whole prologue overlap the previous kernel.
     if (!p.independent) asm volatile("griddepcontrol.wait;" ::: "memory");
     TRACE(1);
+    // Fused all-gather: the peer addresses never change; the epoch was advanced by an earlier
+    // kernel of the stream, so it is read on this side of the wait (through L2, not a cached line).
+    __shared__ uint64_t peer_base[16];
+    uint32_t epoch = 0;
+    if constexpr (GATHER) {
+        if (tid < p.world) peer_base[tid] = p.y_peer_bases[tid] + p.y_offset_bytes;
+        if (!p.independent) asm volatile("ld.relaxed.gpu.global.u32 %0, [%1];" : "=r"(epoch) : "l"(p.epoch_ptr) : "memory");
+    }
 
     if constexpr (PREPARED) {
         // The digit words were produced once by q4_quantize_x_kernel: copy them (and the
@@ -464,7 +470,11 @@ __global__ void __launch_bounds__(512, 1) q4_matvec_stream_kernel(const StreamPa
 
     TRACE(18);
     __syncthreads();
-    if (p.independent) asm volatile("griddepcontrol.wait;" ::: "memory");  // stream order for y
+    if (p.independent) {
+        asm volatile("griddepcontrol.wait;" ::: "memory");  // stream order for y
+        if constexpr (GATHER)
+            asm volatile("ld.relaxed.gpu.global.u32 %0, [%1];" : "=r"(epoch) : "l"(p.epoch_ptr) : "memory");
+    }
     TRACE(19);
     if constexpr (!GATHER) {
         for (uint32_t r = tid; r < my_rows; r += blockDim.x) {
@@ -474,40 +484,16 @@ __global__ void __launch_bounds__(512, 1) q4_matvec_stream_kernel(const StreamPa
         }
     } else {
         // All-gather fused into the epilogue: the slice goes straight into every rank's vector
-        // (plain peer stores over NVLink; no multicast, no TMA on peer memory).
+        // (plain peer stores over NVLink; no multicast, no TMA on peer memory).  Each value
+        // travels with the epoch in the same naturally aligned 8-byte word, so a reader that sees
+        // the epoch sees the value: no fence, no flag exchange, nothing for this CTA to wait for.
         for (uint32_t r = tid; r < my_rows; r += blockDim.x) {
             float sum = part[r * wpr];
             for (uint32_t wv = 1; wv < wpr; ++wv) sum += part[r * wpr + wv];
+            const uint64_t word = ((uint64_t)epoch << 32) | (uint64_t)__float_as_uint(sum);
             for (uint32_t pr = 0; pr < p.world; ++pr) {
-                float* dst = reinterpret_cast<float*>(p.y_peer_bases[pr] + p.y_offset_bytes);
-                dst[p.row_offset + r0 + r] = sum;
-            }
-        }
-        __threadfence_system();  // this thread's peer stores are visible system-wide
-        __syncthreads();
-        if (tid == 0) {
-            const uint32_t done = atomicAdd(&p.local_words[0], 1u);
-            if (done == gridDim.x - 1) {  // last CTA of this rank: the whole slice is out
-                __threadfence_system();
-                p.local_words[0] = 0;     // ready for the next launch (stream order)
-                const uint32_t epoch = ++p.local_words[1];
-                for (uint32_t pr = 0; pr < p.world; ++pr) {
-                    uint32_t* f = reinterpret_cast<uint32_t*>(p.flag_peer_bases[pr] + p.flag_offset_bytes) + p.rank;
-                    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(f), "r"(epoch) : "memory");
-                }
-                // The kernel ends only when every rank's slice has landed here, so anything later
-                // in this stream may read the assembled vector.  Bounded: a rank that never
-                // arrives costs about two seconds and sets an error bit, it does not hang the GPU.
-                const uint32_t* mine = reinterpret_cast<const uint32_t*>(p.flag_peer_bases[p.rank] + p.flag_offset_bytes);
-                for (uint32_t pr = 0; pr < p.world; ++pr) {
-                    uint32_t seen = 0, it = 0;
-                    for (; it < (1u << 22); ++it) {
-                        asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(mine + pr) : "memory");
-                        if ((int32_t)(seen - epoch) >= 0) break;
-                        __nanosleep(200);
-                    }
-                    if (it == (1u << 22) && p.status) atomicOr(p.status, ERR_PEER_WAIT_TIMEOUT);
-                }
+                uint64_t* dst = reinterpret_cast<uint64_t*>(peer_base[pr]) + (p.row_offset + r0 + r);
+                asm volatile("st.relaxed.sys.global.b64 [%0], %1;" ::"l"(dst), "l"(word) : "memory");
             }
         }
     }
@@ -605,9 +591,8 @@ static cudaError_t launch_stream(const uint8_t* q, const float* x, float* y, uin
     void (*kern)(StreamParams) = nullptr;
     if (tune.gather) {
         const GatherArgs& g = *tune.gather;
-        p.y_peer_bases = g.y_peer_bases, p.flag_peer_bases = g.flag_peer_bases;
-        p.y_offset_bytes = g.y_offset_bytes, p.flag_offset_bytes = g.flag_offset_bytes;
-        p.local_words = g.local_words, p.world = g.world, p.rank = g.rank, p.row_offset = g.row_offset;
+        p.y_peer_bases = g.y_peer_bases, p.y_offset_bytes = g.y_offset_bytes, p.epoch_ptr = g.epoch_ptr;
+        p.world = g.world, p.rank = g.rank, p.row_offset = g.row_offset;
         switch (passes) {
             case 1: kern = q4_matvec_stream_kernel<FMT, 1, false, true>; break;
             case 2: kern = q4_matvec_stream_kernel<FMT, 2, false, true>; break;
@@ -644,6 +629,45 @@ static cudaError_t launch_stream(const uint8_t* q, const float* x, float* y, uin
     cfg.attrs = attr;
     cfg.numAttrs = tune.pdl != 0 ? 1 : 0;
     return cudaLaunchKernelEx(&cfg, kern, p);
+}
+
+// Consumer side of the fused all-gather: waits until every (value, epoch) word of `pairs` carries
+// the current epoch and writes the values out as a plain fp32 vector.  Bounded (about two seconds
+// per element that never arrives), then ERR_PEER_WAIT_TIMEOUT and the stale value is written.
+__global__ void gather_finish_kernel(const uint64_t* __restrict__ pairs, const uint32_t* __restrict__ epoch_ptr,
+                                     float* __restrict__ out, uint32_t n, uint32_t* status) {
+    const uint32_t epoch = *epoch_ptr;
+    bool gave_up = false;
+    for (uint32_t i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) {
+        uint64_t w = 0;
+        uint32_t it = gave_up ? (1u << 22) - 1u : 0u;   // after one timeout the rest get a single look
+        for (; it < (1u << 22); ++it) {
+            asm volatile("ld.relaxed.sys.global.b64 %0, [%1];" : "=l"(w) : "l"(pairs + i) : "memory");
+            if ((int32_t)((uint32_t)(w >> 32) - epoch) >= 0) break;
+            __nanosleep(100);
+        }
+        if (it == (1u << 22)) {
+            gave_up = true;
+            if (status) atomicOr(status, ERR_PEER_WAIT_TIMEOUT);
+        }
+        out[i] = __uint_as_float((uint32_t)w);
+    }
+}
+
+__global__ void gather_next_epoch_kernel(uint32_t* epoch_ptr) { *epoch_ptr += 1; }
+
+cudaError_t launch_gather_finish(const uint64_t* pairs, const uint32_t* epoch_ptr, float* out, uint32_t n,
+                                 uint32_t* status, cudaStream_t stream) {
+    if (n == 0) return cudaSuccess;
+    uint32_t blocks = (n + 255) / 256;
+    if (blocks > 592) blocks = 592;
+    gather_finish_kernel<<<blocks, 256, 0, stream>>>(pairs, epoch_ptr, out, n, status);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_gather_next_epoch(uint32_t* epoch_ptr, cudaStream_t stream) {
+    gather_next_epoch_kernel<<<1, 1, 0, stream>>>(epoch_ptr);
+    return cudaGetLastError();
 }
 
 // Stand-alone quantiser: writes what the matvec kernel otherwise builds in shared memory

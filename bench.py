@@ -219,8 +219,8 @@ def run_ours(args):
         if strong:
             w = w[rank * rows_local * row_bytes:(rank + 1) * rows_local * row_bytes]
         weights.append(torch.from_numpy(np.ascontiguousarray(w)).to(dev))
-    # N > 1: the all-gather is fused into the matvec epilogue (peer stores over NVLink + one flag
-    # per rank); `--collective nccl` keeps the plain NCCL all-gather after each call instead.
+    # N > 1: the all-gather is fused into the matvec epilogue (peer stores over NVLink, value and
+    # epoch in one word); `--collective nccl` keeps the plain NCCL all-gather after each call instead.
     gather = None
     collective = "none"
     if world > 1:
@@ -247,6 +247,8 @@ def run_ours(args):
 
     def step(tn=None):
         tn = tuning if tn is None else tn
+        if gather is not None:
+            gather.begin_step()
         for m in range(N_MATRICES):
             if gather is not None:
                 gather.matvec(weights[m], x_dev, N_SB, m, status=status, tuning=tn)
@@ -254,6 +256,8 @@ def run_ours(args):
                 ops.q4k_matvec(weights[m], x_dev, rows_local, N_SB, y=y_local[m], status=status, tuning=tn)
                 if world > 1:
                     sharding.all_gather_rows(y_local[m], rows_global, out=y_full[m])
+        if gather is not None:
+            gather.finish(status)   # every all-gather of the step is complete inside the timed region
 
     # ---- parity spot check against the oracle before timing (checker only) ----
     step()
@@ -407,7 +411,7 @@ def run_ours(args):
         "pct_of_8TBs": round(100.0 * (bytes_per_call_local / (us_per_call * 1e-6)) / 8e12, 2),
         "strict_stream_order": strict,
         "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e,
-        "gpu_launches": calls, "clocks": sampler.summary(),
+        "gpu_launches": calls + (2 * args.steps if gather is not None else 0), "clocks": sampler.summary(),
     }
     print(json.dumps(line), flush=True)
     if world > 1:

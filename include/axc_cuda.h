@@ -230,27 +230,34 @@ int axc_cuda_q4_0_dequant(const void* q, float* w, uint32_t rows, uint32_t n_blo
  * The reference has no multi-GPU path; this is the exchange step of sharding its rows over the
  * GPUs of one node.  Every rank computes `rows_local` rows and stores them at
  * [row_offset, row_offset + rows_local) of EVERY rank's full-length vector through peer-mapped
- * memory (plain stores over NVLink), then the ranks exchange one flag each; the kernel returns
- * only when all slices have arrived in this rank's vector, so later work in the same stream may
- * read it.  The wait is bounded (about two seconds), after which bit 4 of *status is set.
- *   y_peer_bases / flag_peer_bases: DEVICE arrays of `world` addresses (this process's mappings
- *     of each rank's y storage and flag storage; entry `rank` is the local buffer);
- *   y_offset_bytes: where this call's vector (fp32, global row count) starts in the y storage;
- *   flag_offset_bytes: where this call's flag row (uint32[world], zero before first use) starts;
- *   local_words: two uint32 of this rank (zero before first use) tied to that flag row.
- * All ranks must issue the same sequence of calls per flag row.  Reusing a vector needs one
- * other all-gather call in between (double buffering). */
+ * memory (plain stores over NVLink).  A vector is stored as one 8-byte word per global row:
+ * the fp32 value in the low half, the epoch of the step in the high half, written by a single
+ * store, so a reader that finds the epoch has the value.  The producer needs no fence, no flag
+ * and never waits.  Before anything reads an assembled vector, axc_cuda_gather_finish must run
+ * in the same stream: it waits (bounded to about two seconds per missing word, after which bit 4
+ * of *status is set) until every word carries the current epoch and writes the values out as a
+ * plain fp32 vector, so the exchange latency overlaps with the calls in between.
+ *   y_peer_bases: DEVICE array of `world` addresses (this process's mappings of each rank's
+ *     pair storage; entry `rank` is the local buffer; the storage is zero before first use);
+ *   y_offset_bytes: where this call's vector (8 bytes per global row) starts in that storage;
+ *   epoch: this rank's epoch counter (one device uint32, zero before first use), advanced by
+ *     axc_cuda_gather_next_epoch once per step (one step = one pass over the vectors in use).
+ * All ranks issue the same sequence of calls.  A vector may be rewritten once every rank has
+ * finished the step that read it; a caller that cannot guarantee that alternates two vectors. */
 typedef struct axc_gather {
     const uint64_t* y_peer_bases;
-    const uint64_t* flag_peer_bases;
     uint64_t y_offset_bytes;
-    uint64_t flag_offset_bytes;
-    uint32_t* local_words;
+    const uint32_t* epoch;
     uint32_t world, rank, row_offset;
 } axc_gather;
 int axc_cuda_q4k_matvec_allgather(const void* q, const float* x, uint32_t rows_local,
                                   uint32_t n_superblocks, const axc_gather* g, void* stream,
                                   uint32_t* status, const axc_tuning* tuning);
+/* *epoch += 1, in stream order (a one-thread kernel). */
+int axc_cuda_gather_next_epoch(uint32_t* epoch, void* stream);
+/* Consumer side: pairs = this rank's own pair storage (n words), out = n fp32 values. */
+int axc_cuda_gather_finish(const uint64_t* pairs, const uint32_t* epoch, float* out, uint32_t n,
+                           void* stream, uint32_t* status);
 
 /* Launch geometry the matvec launchers would use (no launch). */
 int axc_cuda_q4k_matvec_plan(uint32_t rows, uint32_t n_superblocks, const axc_tuning* tuning,

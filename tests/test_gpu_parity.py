@@ -210,8 +210,9 @@ def test_q4k_ring_refill_path(ops, synth):
 
 
 def test_q4k_fused_allgather_epilogue_single_rank(synth):
-    """The all-gather epilogue with world = 1 (peer table = own buffer): slices land at the row
-    offset of the right slot, flags and epochs advance per call, back-to-back calls are ordered."""
+    """The all-gather epilogue with world = 1 (peer table = own buffer): every slice lands at the
+    row offset of its slot as (value, epoch) words, finish() unpacks exactly the plain matvec's
+    values, and epochs advance per step."""
     from conftest import load_pkg
     coll = load_pkg("collective")
     ops_ = load_pkg("ops")
@@ -220,18 +221,40 @@ def test_q4k_fused_allgather_epilogue_single_rank(synth):
     assert (pg.world, pg.rank, pg.row_offset, pg.rows_local) == (1, 0, 0, rows)
     st = ops_.new_status()
     for it in range(2):
+        pg.begin_step()
+        cases = []
         for slot in range(slots):
             q = synth.q4k_weights(rows, n_sb, 4000 + 10 * it + slot)
             x = synth.activations(n_sb * 256, 4100 + 10 * it + slot)
-            y = pg.matvec(dev(q), dev(x), n_sb, slot, status=st)
+            pg.matvec(dev(q), dev(x), n_sb, slot, status=st,
+                      tuning=ops_.make_tuning(pdl=3 if slot else 2))
+            cases.append((q, x))
+        pg.finish(st)
+        for slot, (q, x) in enumerate(cases):
+            y = pg.vector(slot)
             y_plain = ops_.q4k_matvec(dev(q), dev(x), rows, n_sb)
             assert torch.equal(y, y_plain)
             y_ref = oracle.matvec_rows("q4k", q, x, rows, n_sb)
             _y64, mag = oracle.matvec_rows_f64("q4k", q, x, rows, n_sb)
             assert (np.abs(y.cpu().numpy() - y_ref) / mag).max() <= NORMWISE_TOL
+        assert int(pg.epoch.item()) == it + 1
+        assert ((pg.pairs.cpu().numpy() >> 32) == it + 1).all()    # every word carries the step's epoch
     assert int(st.item()) == 0
-    assert pg.flags.cpu().tolist() == [2] * slots                    # epoch 2 published per slot
-    assert pg.local_words.cpu().tolist() == [0, 2] * slots          # CTA counter reset, epoch 2
+
+
+def test_gather_finish_times_out_without_faulting():
+    """A word whose epoch never arrives: finish() gives up after its bounded wait, sets the
+    peer-wait bit in the status word and leaves the context usable."""
+    from conftest import load_pkg
+    coll = load_pkg("collective")
+    ops_ = load_pkg("ops")
+    pg = coll.PeerGather(8, 1, "cuda")
+    pg.begin_step()          # epoch 1, nothing stores
+    st = ops_.new_status()
+    pg.finish(st)
+    torch.cuda.synchronize()
+    assert int(st.item()) & 4
+    assert torch.zeros(4, device="cuda").sum().item() == 0.0
 
 
 # ---------------------------------------------------------------------------------- Q4_0
