@@ -90,6 +90,7 @@ SYMBOLS = {
     "axc_cuda_kernel_buffer_sizes": (C.c_uint32, [_VP, _U64P, C.c_uint32]),
     "axc_cuda_kernel_cache_key": (None, [_VP, _U64P, _U64P, _U32P]),
     "axc_cuda_kernel_set_strict_order": (None, [_VP, C.c_int]),
+    "axc_cuda_kernel_set_tuning": (None, [_VP, C.POINTER(AxcTuning)]),
     "axc_cuda_dispatch": (C.c_int, [_VP, _VP] + _DISPATCH_TAIL + [C.POINTER(AxcDispatchStats)]),
     "axc_cuda_dispatch_oneshot": (C.c_int, [_VP, C.c_char_p, C.POINTER(AxcBufDesc), C.c_uint32,
                                             C.c_uint32, C.c_uint64, C.c_uint64] + _DISPATCH_TAIL +

@@ -91,6 +91,7 @@ struct axc_kernel {
     uint32_t n_bufs = 0;
     uint32_t pc_total = 0;
     std::atomic<int> strict{0};
+    axc::MatvecTuning tune;  // guarded by mu
     std::mutex mu;  // serialises dispatches on this handle (context.rs:494-519)
     std::vector<Slot> slots;
     uint32_t* status_dev = nullptr;
@@ -307,7 +308,7 @@ int dispatch_locked(axc_ctx* ctx, axc_kernel* k, const uint32_t wg[3], const voi
                     ? axc::launch_q4k_matvec_seq((const uint8_t*)sq.dev, (const float*)sx.dev, (float*)sy.dev, (uint32_t)rows, n, st)
                     : axc::launch_q4_0_matvec_seq((const uint8_t*)sq.dev, (const float*)sx.dev, (float*)sy.dev, (uint32_t)rows, n, st);
         } else {
-            axc::MatvecTuning tune;
+            const axc::MatvecTuning& tune = k->tune;
             e = k->kind == KernelKind::Q4K
                     ? axc::launch_q4k_matvec((const uint8_t*)sq.dev, (const float*)sx.dev, (float*)sy.dev, (uint32_t)rows, n, k->status_dev, st, tune, k->sm_count, nullptr)
                     : axc::launch_q4_0_matvec((const uint8_t*)sq.dev, (const float*)sx.dev, (float*)sy.dev, (uint32_t)rows, n, k->status_dev, st, tune, k->sm_count, nullptr);
@@ -604,6 +605,12 @@ void axc_cuda_kernel_cache_key(const axc_kernel* k, uint64_t* spirv_hash, uint64
 
 void axc_cuda_kernel_set_strict_order(axc_kernel* k, int strict) {
     if (k) k->strict.store(strict ? 1 : 0);
+}
+
+void axc_cuda_kernel_set_tuning(axc_kernel* k, const axc_tuning* tuning) {
+    if (!k) return;
+    std::lock_guard<std::mutex> lock(k->mu);
+    k->tune = to_tuning(tuning);
 }
 
 int axc_cuda_dispatch(axc_ctx* ctx, axc_kernel* k, const uint32_t workgroups[3],

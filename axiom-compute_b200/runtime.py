@@ -287,6 +287,10 @@ class KernelHandle:
         """Run the reference-order kernel (bit-identical y, slow) instead of the fast one."""
         _ffi.lib().axc_cuda_kernel_set_strict_order(self._ptr, 1 if strict else 0)
 
+    def set_tuning(self, tuning) -> None:
+        """Launch tunables (an ``_ffi.AxcTuning`` or None = defaults) for later dispatches."""
+        _ffi.lib().axc_cuda_kernel_set_tuning(self._ptr, C.byref(tuning) if tuning is not None else None)
+
     def drop(self) -> None:
         if self._ptr:
             _ffi.lib().axc_cuda_kernel_release(self._ptr)

@@ -141,6 +141,13 @@ void axc_cuda_kernel_cache_key(const axc_kernel* k, uint64_t* spirv_hash, uint64
 /* Strict mode: when non-zero the handle runs the reference-order kernel whose y is
  * bit-identical to the CPU reference (one thread per row; slow).  Default 0. */
 void axc_cuda_kernel_set_strict_order(axc_kernel* k, int strict);
+/* Launch tunables the handle's later dispatches use (struct axc_tuning below; NULL = defaults).
+ * This is what a grid search over the kernel's tunables sets per variant: the reference's
+ * `assignments` of strategy holes (crates/axc-optimize/src/enumerator.rs:44-61) select a
+ * compiled variant, here they select launch geometry of the one ahead-of-time kernel.  A
+ * combination the launcher cannot realise makes the dispatch return QueueSubmitFailed. */
+struct axc_tuning;
+void axc_cuda_kernel_set_tuning(axc_kernel* k, const struct axc_tuning* tuning);
 
 /* ---- dispatch (context.rs:498-547, kernel_handle.rs:295-393,410-738, dispatch.rs:56-132) ----
  *
