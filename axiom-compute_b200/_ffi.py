@@ -65,6 +65,11 @@ class AxcGather(C.Structure):
                 ("world", C.c_uint32), ("rank", C.c_uint32), ("row_offset", C.c_uint32)]
 
 
+class AxcXSrc(C.Structure):
+    _fields_ = [("x", C.c_void_p), ("x2", C.c_void_p), ("x_pairs", C.c_void_p), ("x2_pairs", C.c_void_p),
+                ("epoch", C.c_void_p), ("unit_rms", C.c_uint32)]
+
+
 # Every symbol include/axc_cuda.h declares: name -> (restype, argtypes)
 _VP = C.c_void_p
 _U32P = C.POINTER(C.c_uint32)
@@ -112,6 +117,8 @@ SYMBOLS = {
                                            C.POINTER(C.c_int32)]),
     "axc_cuda_q4k_matvec_allgather": (C.c_int, [_VP, _VP, C.c_uint32, C.c_uint32, C.POINTER(AxcGather), _VP, _VP,
                                                 C.POINTER(AxcTuning)]),
+    "axc_cuda_q4k_matvec_fused": (C.c_int, [_VP, C.POINTER(AxcXSrc), _VP, C.c_uint32, C.c_uint32,
+                                            C.POINTER(AxcGather), _VP, _VP, C.POINTER(AxcTuning)]),
     "axc_cuda_gather_next_epoch": (C.c_int, [_VP, _VP]),
     "axc_cuda_gather_finish": (C.c_int, [_VP, _VP, _VP, C.c_uint32, _VP, _VP]),
     "axc_cuda_q4k_matvec_static": (C.c_int, [_VP, _VP, _VP, C.c_uint32, C.c_uint32, _VP]),

@@ -14,6 +14,19 @@ struct GatherArgs {
     uint32_t world, rank, row_offset;
 };
 
+// Where the streaming matvec takes its activations from when they are not one plain vector:
+// x = a [+ b]; a and b are each a plain fp32 vector or a vector of (value, epoch) words written by
+// the all-gather epilogue of an earlier call (the reader polls, bounded, until the epoch read
+// from `epoch_ptr` has arrived); unit_rms divides x by sqrt(mean(x^2)).
+struct XSource {
+    const float* x = nullptr;
+    const float* x2 = nullptr;
+    const uint64_t* x_pairs = nullptr;
+    const uint64_t* x2_pairs = nullptr;
+    const uint32_t* epoch_ptr = nullptr;
+    int unit_rms = 0;
+};
+
 // Tunables of the streaming matvec kernels.  0 = let the launcher choose.
 struct MatvecTuning {
     int ctas_per_sm = 0;  // resident CTAs per SM the grid is sized for
@@ -26,6 +39,7 @@ struct MatvecTuning {
     int dry_run = 0;      // compute the launch geometry only, launch nothing
     const void* x_prepared = nullptr;  // activations already quantised by launch_q4_quantize_x
     const GatherArgs* gather = nullptr;  // all-gather fused into the epilogue (y is ignored)
+    const XSource* xsrc = nullptr;       // fused activation source (Q4_K_M only; x is ignored)
 };
 
 struct LaunchInfo {

@@ -783,6 +783,37 @@ int axc_cuda_q4k_matvec_allgather(const void* q, const float* x, uint32_t rows_l
     return launch_result(axc::launch_q4k_matvec((const uint8_t*)q, x, nullptr, rows_local, n_superblocks, status, (cudaStream_t)stream, t, sm_count_of_current_device(), nullptr));
 }
 
+int axc_cuda_q4k_matvec_fused(const void* q, const axc_xsrc* xs, float* y, uint32_t rows,
+                              uint32_t n_superblocks, const axc_gather* g, void* stream,
+                              uint32_t* status, const axc_tuning* tuning) {
+    clear_error();
+    if (rows == 0) return AXC_OK;
+    if (!xs || (!xs->x == !xs->x_pairs) || (xs->x2 && xs->x2_pairs))
+        return fail(AXC_ERR_INVALID_ARGUMENT, "x source: exactly one of x / x_pairs, at most one of x2 / x2_pairs");
+    if ((xs->x_pairs || xs->x2_pairs) && !xs->epoch)
+        return fail(AXC_ERR_INVALID_ARGUMENT, "x source: (value, epoch) vectors need the epoch counter");
+    if (!q || (((uintptr_t)q | (uintptr_t)xs->x | (uintptr_t)xs->x2 | (uintptr_t)xs->x_pairs | (uintptr_t)xs->x2_pairs) & 15u))
+        return fail(AXC_ERR_INVALID_ARGUMENT, "q and the x sources must be 16-byte aligned (q non-null)");
+    if (n_superblocks == 0 || n_superblocks > 128)
+        return fail(AXC_ERR_INVALID_ARGUMENT, "the fused matvec serves rows of 1..128 superblocks");
+    if (!g && (!y || ((uintptr_t)y & 15u)))
+        return fail(AXC_ERR_INVALID_ARGUMENT, "y must be non-null and 16-byte aligned when no all-gather is given");
+    axc::GatherArgs ga{};
+    axc::MatvecTuning t = to_tuning(tuning);
+    if (g) {
+        if (!g->y_peer_bases || !g->epoch || g->world == 0 || g->world > 16 || g->rank >= g->world || (g->y_offset_bytes & 7u))
+            return fail(AXC_ERR_INVALID_ARGUMENT, "incomplete all-gather description");
+        ga.y_peer_bases = g->y_peer_bases, ga.y_offset_bytes = g->y_offset_bytes, ga.epoch_ptr = g->epoch;
+        ga.world = g->world, ga.rank = g->rank, ga.row_offset = g->row_offset;
+        t.gather = &ga;
+    }
+    axc::XSource src;
+    src.x = xs->x, src.x2 = xs->x2, src.x_pairs = xs->x_pairs, src.x2_pairs = xs->x2_pairs;
+    src.epoch_ptr = xs->epoch, src.unit_rms = xs->unit_rms ? 1 : 0;
+    t.xsrc = &src;
+    return launch_result(axc::launch_q4k_matvec((const uint8_t*)q, nullptr, y, rows, n_superblocks, status, (cudaStream_t)stream, t, sm_count_of_current_device(), nullptr));
+}
+
 int axc_cuda_gather_next_epoch(uint32_t* epoch, void* stream) {
     clear_error();
     if (!epoch) return fail(AXC_ERR_INVALID_ARGUMENT, "null epoch counter");

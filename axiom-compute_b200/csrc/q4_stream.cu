@@ -55,6 +55,14 @@ struct StreamParams {
     const uint8_t* q;
     const float* x;
     const void* x_prepared;  // digit words + metadata made by q4_quantize_x_kernel (PREPARED kernels)
+    // Fused x source (XFUSE kernels): x = a [+ b], each either a plain fp32 vector or a vector
+    // of (value, epoch) words written by the all-gather epilogue of an earlier call; with
+    // x_unit_rms the result is the matvec of x / sqrt(mean(x^2)).
+    const float* x2;
+    const uint64_t* x_pairs;
+    const uint64_t* x2_pairs;
+    const uint32_t* x_epoch_ptr;
+    uint32_t x_unit_rms;
     float* y;
     uint32_t* status;
     uint32_t rows;
@@ -243,11 +251,13 @@ __device__ __forceinline__ float warp_reduce_transposed(const float (&v)[PASSES]
 // xs[k][pos] with an XOR swizzle so that these stores and the per-thread reads of the matvec
 // are free of shared-memory bank conflicts; xm[pos] = (sum of columns 0..31, sum of columns
 // 32..63, two factors of 2^(e-21)).  `nthreads` is a multiple of 32; all threads must call.
-__device__ __forceinline__ void quantize_x_positions(const float* __restrict__ x, uint4* xs, float4* xm,
-                                                     uint32_t n_pos, uint32_t pos_end, uint32_t pitch,
-                                                     uint32_t tid, uint32_t nthreads) {
+// `load4(i)` returns columns 4i..4i+3.  Returns this thread's share of sum(x^2).
+template <class Load4>
+__device__ __forceinline__ float quantize_x_positions_from(Load4 load4, uint4* xs, float4* xm,
+                                                           uint32_t n_pos, uint32_t pos_end, uint32_t pitch,
+                                                           uint32_t tid, uint32_t nthreads) {
+    float sumsq = 0.0f;
     {
-        const float4* xg = reinterpret_cast<const float4*>(x);
         constexpr uint32_t FULL = 0xFFFFFFFFu;
         const uint32_t qt = tid & 3u;
         for (uint32_t pos = tid >> 2; pos < pos_end; pos += nthreads >> 2) {
@@ -255,13 +265,14 @@ __device__ __forceinline__ void quantize_x_positions(const float* __restrict__ x
             float4 v[4];
 #pragma unroll
             for (int u = 0; u < 4; ++u)
-                v[u] = valid ? __ldg(xg + pos * 16 + qt * 4 + u) : make_float4(0.f, 0.f, 0.f, 0.f);
+                v[u] = valid ? load4(pos * 16 + qt * 4 + u) : make_float4(0.f, 0.f, 0.f, 0.f);
             // largest finite |x| of the chunk (NaNs are ignored by fmaxf) and the half sums
             float m = 0.0f, s = 0.0f;
 #pragma unroll
             for (int u = 0; u < 4; ++u) {
                 m = fmaxf(m, fmaxf(fmaxf(fabsf(v[u].x), fabsf(v[u].y)), fmaxf(fabsf(v[u].z), fabsf(v[u].w))));
                 s += (v[u].x + v[u].y) + (v[u].z + v[u].w);
+                sumsq += (v[u].x * v[u].x + v[u].y * v[u].y) + (v[u].z * v[u].z + v[u].w * v[u].w);
             }
             m = fmaxf(m, __shfl_xor_sync(FULL, m, 1));
             m = fmaxf(m, __shfl_xor_sync(FULL, m, 2));
@@ -286,9 +297,41 @@ __device__ __forceinline__ void quantize_x_positions(const float* __restrict__ x
             }
         }
     }
+    return sumsq;
 }
 
-template <int FMT, int PASSES, bool PREPARED, bool GATHER>
+__device__ __forceinline__ void quantize_x_positions(const float* __restrict__ x, uint4* xs, float4* xm,
+                                                     uint32_t n_pos, uint32_t pos_end, uint32_t pitch,
+                                                     uint32_t tid, uint32_t nthreads) {
+    const float4* xg = reinterpret_cast<const float4*>(x);
+    (void)quantize_x_positions_from([&](uint32_t i) { return __ldg(xg + i); }, xs, xm, n_pos, pos_end, pitch,
+                                    tid, nthreads);
+}
+
+// Four columns of a (value, epoch) vector: polls (bypassing L1) until all four words carry an
+// epoch >= `epoch`.  Bounded; after one timeout the thread only looks once at later words.
+__device__ __forceinline__ float4 load_pairs4(const uint64_t* base, uint32_t i, uint32_t epoch, bool& gave_up) {
+    const uint4* src = reinterpret_cast<const uint4*>(base) + 2 * (size_t)i;
+    uint4 a, b;
+    uint32_t it = gave_up ? (1u << 20) - 1u : 0u;
+    for (;;) {
+        asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];"
+                     : "=r"(a.x), "=r"(a.y), "=r"(a.z), "=r"(a.w) : "l"(src) : "memory");
+        asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];"
+                     : "=r"(b.x), "=r"(b.y), "=r"(b.z), "=r"(b.w) : "l"(src + 1) : "memory");
+        const bool ok = (int32_t)(a.y - epoch) >= 0 && (int32_t)(a.w - epoch) >= 0 &&
+                        (int32_t)(b.y - epoch) >= 0 && (int32_t)(b.w - epoch) >= 0;
+        if (ok) break;
+        if (++it >= (1u << 20)) {
+            gave_up = true;
+            break;
+        }
+        __nanosleep(64);
+    }
+    return make_float4(__uint_as_float(a.x), __uint_as_float(a.z), __uint_as_float(b.x), __uint_as_float(b.z));
+}
+
+template <int FMT, int PASSES, bool PREPARED, bool GATHER, bool XFUSE>
 __global__ void __launch_bounds__(512, 1) q4_matvec_stream_kernel(const StreamParams p) {
     extern __shared__ __align__(128) uint8_t smem[];
     const uint32_t tid = threadIdx.x;
@@ -371,6 +414,7 @@ __global__ void __launch_bounds__(512, 1) q4_matvec_stream_kernel(const StreamPa
     // Fused all-gather: the peer addresses never change; the epoch was advanced by an earlier
     // kernel of the stream, so it is read on this side of the wait (through L2, not a cached line).
     __shared__ uint64_t peer_base[16];
+    __shared__ float sumsq_part[16];
     uint32_t epoch = 0;
     if constexpr (GATHER) {
         if (tid < p.world) peer_base[tid] = p.y_peer_bases[tid] + p.y_offset_bytes;
@@ -382,6 +426,27 @@ __global__ void __launch_bounds__(512, 1) q4_matvec_stream_kernel(const StreamPa
         // per-position sums and scales that follow them) as they are.
         const uint4* src = reinterpret_cast<const uint4*>(p.x_prepared);
         for (uint32_t i = tid; i < 17u * p.x_pitch; i += blockDim.x) xs[i] = __ldg(src + i);
+    } else if constexpr (XFUSE) {
+        uint32_t x_epoch = 0;
+        if (p.x_pairs || p.x2_pairs)
+            asm volatile("ld.relaxed.gpu.global.u32 %0, [%1];" : "=r"(x_epoch) : "l"(p.x_epoch_ptr) : "memory");
+        bool gave_up = false;
+        const float4* xa = reinterpret_cast<const float4*>(p.x);
+        const float4* xb = reinterpret_cast<const float4*>(p.x2);
+        float sq = quantize_x_positions_from(
+            [&](uint32_t i) {
+                float4 v = p.x_pairs ? load_pairs4(p.x_pairs, i, x_epoch, gave_up) : __ldg(xa + i);
+                if (p.x2_pairs || xb) {
+                    const float4 w = p.x2_pairs ? load_pairs4(p.x2_pairs, i, x_epoch, gave_up) : __ldg(xb + i);
+                    v.x += w.x, v.y += w.y, v.z += w.z, v.w += w.w;
+                }
+                return v;
+            },
+            xs, xm, p.n_pos, p.x_pos_end, p.x_pitch, tid, blockDim.x);
+        if (gave_up && p.status) atomicOr(p.status, ERR_PEER_WAIT_TIMEOUT);
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) sq += __shfl_xor_sync(0xFFFFFFFFu, sq, o);
+        if (lane == 0) sumsq_part[warp] = sq;
     } else {
         quantize_x_positions(p.x, xs, xm, p.n_pos, p.x_pos_end, p.x_pitch, tid, blockDim.x);
     }
@@ -476,10 +541,20 @@ __global__ void __launch_bounds__(512, 1) q4_matvec_stream_kernel(const StreamPa
             asm volatile("ld.relaxed.gpu.global.u32 %0, [%1];" : "=r"(epoch) : "l"(p.epoch_ptr) : "memory");
     }
     TRACE(19);
+    // x / sqrt(mean(x^2)) as input = the plain result times 1 / sqrt(mean(x^2)).
+    float out_scale = 1.0f;
+    if constexpr (XFUSE) {
+        if (p.x_unit_rms) {
+            float tot = 0.0f;
+            for (uint32_t w = 0; w < n_warps; ++w) tot += sumsq_part[w];
+            out_scale = 1.0f / sqrtf(tot / (float)(p.n_pos * 64u));
+        }
+    }
     if constexpr (!GATHER) {
         for (uint32_t r = tid; r < my_rows; r += blockDim.x) {
             float sum = part[r * wpr];
             for (uint32_t wv = 1; wv < wpr; ++wv) sum += part[r * wpr + wv];
+            if constexpr (XFUSE) sum *= out_scale;
             p.y[r0 + r] = sum;
         }
     } else {
@@ -490,6 +565,7 @@ __global__ void __launch_bounds__(512, 1) q4_matvec_stream_kernel(const StreamPa
         for (uint32_t r = tid; r < my_rows; r += blockDim.x) {
             float sum = part[r * wpr];
             for (uint32_t wv = 1; wv < wpr; ++wv) sum += part[r * wpr + wv];
+            if constexpr (XFUSE) sum *= out_scale;
             const uint64_t word = ((uint64_t)epoch << 32) | (uint64_t)__float_as_uint(sum);
             for (uint32_t pr = 0; pr < p.world; ++pr) {
                 uint64_t* dst = reinterpret_cast<uint64_t*>(peer_base[pr]) + (p.row_offset + r0 + r);
@@ -593,22 +669,44 @@ static cudaError_t launch_stream(const uint8_t* q, const float* x, float* y, uin
         const GatherArgs& g = *tune.gather;
         p.y_peer_bases = g.y_peer_bases, p.y_offset_bytes = g.y_offset_bytes, p.epoch_ptr = g.epoch_ptr;
         p.world = g.world, p.rank = g.rank, p.row_offset = g.row_offset;
+    }
+    if (tune.xsrc) {
+        if (FMT != FMT_Q4K || tune.x_prepared) return cudaErrorInvalidValue;
+        const XSource& s = *tune.xsrc;
+        p.x = s.x, p.x2 = s.x2, p.x_pairs = s.x_pairs, p.x2_pairs = s.x2_pairs;
+        p.x_epoch_ptr = s.epoch_ptr, p.x_unit_rms = s.unit_rms ? 1u : 0u;
+        if constexpr (FMT == FMT_Q4K) {
+            if (tune.gather) {
+                switch (passes) {
+                    case 1: kern = q4_matvec_stream_kernel<FMT, 1, false, true, true>; break;
+                    case 2: kern = q4_matvec_stream_kernel<FMT, 2, false, true, true>; break;
+                    default: kern = q4_matvec_stream_kernel<FMT, 4, false, true, true>; break;
+                }
+            } else {
+                switch (passes) {
+                    case 1: kern = q4_matvec_stream_kernel<FMT, 1, false, false, true>; break;
+                    case 2: kern = q4_matvec_stream_kernel<FMT, 2, false, false, true>; break;
+                    default: kern = q4_matvec_stream_kernel<FMT, 4, false, false, true>; break;
+                }
+            }
+        }
+    } else if (tune.gather) {
         switch (passes) {
-            case 1: kern = q4_matvec_stream_kernel<FMT, 1, false, true>; break;
-            case 2: kern = q4_matvec_stream_kernel<FMT, 2, false, true>; break;
-            default: kern = q4_matvec_stream_kernel<FMT, 4, false, true>; break;
+            case 1: kern = q4_matvec_stream_kernel<FMT, 1, false, true, false>; break;
+            case 2: kern = q4_matvec_stream_kernel<FMT, 2, false, true, false>; break;
+            default: kern = q4_matvec_stream_kernel<FMT, 4, false, true, false>; break;
         }
     } else if (tune.x_prepared) {
         switch (passes) {
-            case 1: kern = q4_matvec_stream_kernel<FMT, 1, true, false>; break;
-            case 2: kern = q4_matvec_stream_kernel<FMT, 2, true, false>; break;
-            default: kern = q4_matvec_stream_kernel<FMT, 4, true, false>; break;
+            case 1: kern = q4_matvec_stream_kernel<FMT, 1, true, false, false>; break;
+            case 2: kern = q4_matvec_stream_kernel<FMT, 2, true, false, false>; break;
+            default: kern = q4_matvec_stream_kernel<FMT, 4, true, false, false>; break;
         }
     } else {
         switch (passes) {
-            case 1: kern = q4_matvec_stream_kernel<FMT, 1, false, false>; break;
-            case 2: kern = q4_matvec_stream_kernel<FMT, 2, false, false>; break;
-            default: kern = q4_matvec_stream_kernel<FMT, 4, false, false>; break;
+            case 1: kern = q4_matvec_stream_kernel<FMT, 1, false, false, false>; break;
+            case 2: kern = q4_matvec_stream_kernel<FMT, 2, false, false, false>; break;
+            default: kern = q4_matvec_stream_kernel<FMT, 4, false, false, false>; break;
         }
     }
     if (info) {

@@ -1,0 +1,223 @@
+"""Decode sweep over a stack of Q4_K_M linear layers (the 70B-shaped workload).
+
+The reference has no model; the sweep is this backend's end-to-end use of its matvec: one
+token's pass through ``layers`` blocks of seven linears with the dataflow
+
+    q, k, v = Wq h, Wk h, Wv h            (k and v are only checksummed)
+    o       = Wo   . unitRMS(q)
+    g, u    = Wgate . unitRMS(o),  Wup . unitRMS(o)
+    d       = Wdown . unitRMS(g + u)
+    h      <- unitRMS(d)                   unitRMS(v) = v / sqrt(mean(v^2)), fp32
+
+Every elementwise step is folded into the matvec that consumes it (``axc_cuda_q4k_matvec_fused``:
+x = a [+ b], unit RMS as one output scale), Wq/Wk/Wv and Wgate/Wup are stored as one matrix each,
+so a layer is four launches.  With more than one GPU every linear is row-sharded and its
+all-gather is fused into the producing kernel's epilogue; the consuming kernel polls the
+(value, epoch) words itself, so there is no collective launch between dependent linears.
+
+Weights are synthetic (uniform nibbles and scale bytes, d and dmin = f16(|N(0,1)| * 0.01)),
+generated on the device in eight row chunks per linear so that the global matrices are the same
+for 1, 2, 4 and 8 ranks.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from dataclasses import dataclass
+from typing import List, Optional
+
+import torch
+
+from . import _ffi
+from .runtime import _raise_for
+
+CHUNKS = 8   # generation granularity along rows = the largest supported world size
+
+
+@dataclass(frozen=True)
+class SweepShape:
+    hidden: int
+    kv: int
+    ffn: int
+    layers: int
+
+    @property
+    def linears(self):
+        """(name, rows, K) of the four launches of a layer."""
+        return (("qkv", self.hidden + 2 * self.kv, self.hidden), ("o", self.hidden, self.hidden),
+                ("gate_up", 2 * self.ffn, self.hidden), ("down", self.hidden, self.ffn))
+
+    @property
+    def weights_per_layer(self) -> int:
+        return sum(r * k for _n, r, k in self.linears)
+
+    @property
+    def bytes_per_layer(self) -> int:
+        return self.weights_per_layer // 256 * 144
+
+    @property
+    def vector_words_per_layer(self) -> int:
+        return sum(r for _n, r, _k in self.linears)
+
+
+LLAMA_70B = SweepShape(hidden=8192, kv=1024, ffn=28672, layers=80)
+
+
+def synth_chunk(rows: int, n_sb: int, seed: int, device) -> torch.Tensor:
+    """`rows` rows of well-formed Q4_K_M superblocks, generated on `device`."""
+    g = torch.Generator(device=device)
+    g.manual_seed(int(seed))
+    nblk = rows * n_sb
+    q = torch.randint(0, 256, (nblk, 144), dtype=torch.uint8, device=device, generator=g)
+    hdr = (torch.randn((nblk, 2), device=device, generator=g).abs() * 0.01).to(torch.float16)
+    q[:, :4] = hdr.view(torch.uint8)
+    return q.view(-1)
+
+
+class DecodeSweep:
+    """One rank's share of the stack plus the buffers and launches of a token."""
+
+    def __init__(self, shape: SweepShape, device, seed: int = 0xA0C0 + 4 * 16, group=None, tuning=None):
+        self.shape, self.device = shape, torch.device(device)
+        self.world, self.rank = 1, 0
+        self.tuning = tuning
+        dist_on = group is not None or (torch.distributed.is_available() and torch.distributed.is_initialized()
+                                        and torch.distributed.get_world_size() > 1)
+        if dist_on:
+            import torch.distributed as dist
+            group = group if group is not None else dist.group.WORLD
+            self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
+        if CHUNKS % self.world:
+            raise ValueError(f"world size must divide {CHUNKS}")
+        for _n, rows, k in shape.linears:
+            if rows % CHUNKS or k % 256 or k // 256 > 128:
+                raise ValueError("every linear needs rows divisible by 8 and K a multiple of 256 up to 32768")
+        per = CHUNKS // self.world
+        # weights[layer][j]: this rank's contiguous rows of linear j
+        self.weights: List[List[torch.Tensor]] = []
+        for layer in range(shape.layers):
+            row = []
+            for j, (_n, rows, k) in enumerate(shape.linears):
+                parts = [synth_chunk(rows // CHUNKS, k // 256, seed + (layer * 4 + j) * CHUNKS + c, self.device)
+                         for c in range(self.rank * per, (self.rank + 1) * per)]
+                row.append(torch.cat(parts) if len(parts) > 1 else parts[0])
+            self.weights.append(row)
+        # vectors: every linear's full output, per layer (k and v stay available for the checksum)
+        words = shape.vector_words_per_layer * shape.layers
+        self.offsets = []   # word offset of linear j of layer l
+        off = 0
+        for layer in range(shape.layers):
+            o = []
+            for _n, rows, _k in shape.linears:
+                o.append(off)
+                off += rows
+            self.offsets.append(o)
+        self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
+        self.epoch = torch.zeros(1, dtype=torch.int32, device=self.device)
+        self.h = torch.zeros(shape.hidden, dtype=torch.float32, device=self.device)     # token input (plain)
+        self.d_last = torch.zeros(shape.hidden, dtype=torch.float32, device=self.device)
+        if self.world > 1:
+            import torch.distributed as dist
+            import torch.distributed._symmetric_memory as symm_mem
+            self.pairs = symm_mem.empty(words, dtype=torch.int64, device=self.device)
+            self.pairs.zero_()
+            self._handle = symm_mem.rendezvous(self.pairs, group)
+            ptrs = list(self._handle.buffer_ptrs)
+            torch.cuda.synchronize(self.device)
+            dist.barrier(group)
+            self.ptr_table = torch.tensor(ptrs, dtype=torch.int64, device=self.device)
+            self.vec = None
+        else:
+            self.pairs = None
+            self.vec = torch.zeros(words, dtype=torch.float32, device=self.device)
+        self.launches_per_token = 4 * shape.layers + (3 if self.world > 1 else 1)
+
+    # -- helpers ---------------------------------------------------------------------------
+    def _stream(self) -> int:
+        return int(torch.cuda.current_stream(self.device).cuda_stream)
+
+    def _linear(self, layer: int, j: int, xsrc: "_ffi.AxcXSrc") -> None:
+        _n, rows, k = self.shape.linears[j]
+        rows_local = rows // self.world
+        w = self.weights[layer][j]
+        off = self.offsets[layer][j]
+        st = self.status.data_ptr()
+        tn = C.byref(self.tuning) if self.tuning is not None else None
+        if self.world > 1:
+            g = _ffi.AxcGather(self.ptr_table.data_ptr(), off * 8, self.epoch.data_ptr(), self.world, self.rank,
+                               self.rank * rows_local)
+            rc = _ffi.lib().axc_cuda_q4k_matvec_fused(w.data_ptr(), C.byref(xsrc), None, rows_local, k // 256,
+                                                      C.byref(g), self._stream(), st, tn)
+        else:
+            rc = _ffi.lib().axc_cuda_q4k_matvec_fused(w.data_ptr(), C.byref(xsrc), self.vec.data_ptr() + off * 4,
+                                                      rows_local, k // 256, None, self._stream(), st, tn)
+        _raise_for(rc)
+
+    def _src(self, layer: int, j: int, word: int = 0, second: Optional[int] = None, rms: bool = True):
+        """x source = output of linear j of `layer` starting at `word` (+ the vector at `second`)."""
+        base = self.offsets[layer][j] + word
+        if self.world > 1:
+            p = self.pairs.data_ptr()
+            return _ffi.AxcXSrc(None, None, p + base * 8,
+                                None if second is None else p + (self.offsets[layer][j] + second) * 8,
+                                self.epoch.data_ptr(), 1 if rms else 0)
+        p = self.vec.data_ptr()
+        return _ffi.AxcXSrc(p + base * 4, None if second is None else p + (self.offsets[layer][j] + second) * 4,
+                            None, None, None, 1 if rms else 0)
+
+    # -- one token --------------------------------------------------------------------------
+    def token(self, normalise_input: bool = True) -> None:
+        """Enqueue one token: reads ``self.h`` (normalised first unless told otherwise, which is
+        how the previous token's d becomes this token's h), leaves the last layer's d in
+        ``self.d_last`` and every linear's output in the vector store."""
+        sh = self.shape
+        with torch.cuda.device(self.device):
+            if self.world > 1:
+                _raise_for(_ffi.lib().axc_cuda_gather_next_epoch(self.epoch.data_ptr(), self._stream()))
+            for layer in range(sh.layers):
+                if layer == 0:
+                    x = _ffi.AxcXSrc(self.h.data_ptr(), None, None, None, None, 1 if normalise_input else 0)
+                else:
+                    x = self._src(layer - 1, 3)                         # h = unitRMS(d of the layer before)
+                self._linear(layer, 0, x)                               # q, k, v
+                self._linear(layer, 1, self._src(layer, 0))             # o = Wo . unitRMS(q): first `hidden` words
+                self._linear(layer, 2, self._src(layer, 1))             # g, u
+                self._linear(layer, 3, self._src(layer, 2, 0, sh.ffn))  # d = Wdown . unitRMS(g + u)
+            last = self.offsets[sh.layers - 1][3]
+            if self.world > 1:
+                _raise_for(_ffi.lib().axc_cuda_gather_finish(
+                    self.pairs.data_ptr() + last * 8, self.epoch.data_ptr(), self.d_last.data_ptr(), sh.hidden,
+                    self._stream(), self.status.data_ptr()))
+                # k and v of every layer must also be complete on this rank before they are read
+                _raise_for(_ffi.lib().axc_cuda_gather_finish(
+                    self.pairs.data_ptr(), self.epoch.data_ptr(), self._plain_store().data_ptr(),
+                    sh.vector_words_per_layer * sh.layers, self._stream(), self.status.data_ptr()))
+            else:
+                self.d_last.copy_(self.vec[last:last + sh.hidden])
+
+    def _plain_store(self) -> torch.Tensor:
+        if self.vec is None:
+            self.vec = torch.zeros(self.shape.vector_words_per_layer * self.shape.layers, dtype=torch.float32,
+                                   device=self.device)
+        return self.vec
+
+    def advance(self) -> None:
+        """h of the next token = d of this one (normalised by the next token's first launch)."""
+        self.h.copy_(self.d_last)
+
+    # -- results ----------------------------------------------------------------------------
+    def output(self, layer: int, j: int) -> torch.Tensor:
+        """Full output vector of linear j of `layer` (after ``token()`` has completed)."""
+        off = self.offsets[layer][j]
+        return self._plain_store()[off:off + self.shape.linears[j][1]]
+
+    def kv_checksum(self) -> torch.Tensor:
+        """Sum of every layer's k and v entries (fp64, on the device)."""
+        sh = self.shape
+        per = sh.vector_words_per_layer
+        v = self._plain_store().view(sh.layers, per)[:, sh.hidden:sh.hidden + 2 * sh.kv]
+        return v.double().sum()
+
+    def hidden_out(self) -> torch.Tensor:
+        """h after the token: unitRMS(d of the last layer)."""
+        d = self.d_last
+        return d / torch.sqrt(torch.mean(d * d))

@@ -260,6 +260,25 @@ typedef struct axc_gather {
 int axc_cuda_q4k_matvec_allgather(const void* q, const float* x, uint32_t rows_local,
                                   uint32_t n_superblocks, const axc_gather* g, void* stream,
                                   uint32_t* status, const axc_tuning* tuning);
+/* Q4_K_M matvec whose activations are assembled inside the kernel: x = a [+ b], where a and b
+ * are each a plain fp32 vector (x, x2) or a vector of (value, epoch) words that the all-gather
+ * epilogue of an earlier call wrote (x_pairs, x2_pairs: the kernel itself polls, bounded, until
+ * every word carries the epoch read from `epoch`, so no separate finish launch is needed
+ * between dependent calls); with unit_rms != 0 the result is the matvec of x / sqrt(mean(x^2))
+ * (fp32).  y receives the rows when g is NULL; with g the rows go into every rank's vector as
+ * for axc_cuda_q4k_matvec_allgather.  No counterpart in the reference (it has neither a
+ * multi-GPU path nor a model); this is the linear layer of the 70B-shaped decode sweep. */
+typedef struct axc_xsrc {
+    const float* x;
+    const float* x2;
+    const uint64_t* x_pairs;
+    const uint64_t* x2_pairs;
+    const uint32_t* epoch;
+    uint32_t unit_rms;
+} axc_xsrc;
+int axc_cuda_q4k_matvec_fused(const void* q, const axc_xsrc* xs, float* y, uint32_t rows,
+                              uint32_t n_superblocks, const axc_gather* g, void* stream,
+                              uint32_t* status, const axc_tuning* tuning);
 /* *epoch += 1, in stream order (a one-thread kernel). */
 int axc_cuda_gather_next_epoch(uint32_t* epoch, void* stream);
 /* Consumer side: pairs = this rank's own pair storage (n words), out = n fp32 values. */

@@ -215,6 +215,35 @@ def q4km_prefill(q, a, m_rows: int, n_rows: int, n_sb: int, threads: int = 0) ->
     return c
 
 
+def unit_rms(v) -> np.ndarray:
+    """v / sqrt(mean(v^2)) in fp32 (the sweep's normalisation; no counterpart in the reference)."""
+    v = _f32(v)
+    ms = np.float32(np.sum(v * v, dtype=np.float32) / np.float32(v.size))
+    return (v / np.float32(np.sqrt(ms))).astype(np.float32)
+
+
+def decode_token(weights, hidden: int, kv: int, ffn: int, h, normalise_input: bool = True, threads: int = 0):
+    """One token of the decode sweep on the CPU, every linear through the reference-order matvec.
+
+    weights[layer] = (qkv, o, gate_up, down) Q4_K_M byte arrays of shapes (hidden + 2 kv, hidden),
+    (hidden, hidden), (2 ffn, hidden), (hidden, ffn).  Dataflow: q,k,v = W h; o = Wo unitRMS(q);
+    g,u = W unitRMS(o); d = Wdown unitRMS(g + u); h <- unitRMS(d).  Returns (outputs, d of the last
+    layer, h after the token, sum of all k and v entries in fp64); outputs[layer] = the four vectors.
+    """
+    h = _f32(h)
+    x = unit_rms(h) if normalise_input else h
+    outs, ksum, d = [], 0.0, None
+    for qkv_w, o_w, gu_w, down_w in weights:
+        qkv = matvec_rows("q4k", qkv_w, x, hidden + 2 * kv, hidden // 256, threads)
+        o = matvec_rows("q4k", o_w, unit_rms(qkv[:hidden]), hidden, hidden // 256, threads)
+        gu = matvec_rows("q4k", gu_w, unit_rms(o), 2 * ffn, hidden // 256, threads)
+        d = matvec_rows("q4k", down_w, unit_rms(gu[:ffn] + gu[ffn:]), hidden, ffn // 256, threads)
+        ksum += float(np.sum(qkv[hidden:].astype(np.float64)))
+        outs.append((qkv, o, gu, d))
+        x = unit_rms(d)
+    return outs, d, x, ksum
+
+
 def generate_q4km_test_data(n_superblocks: int, seed: int):
     """The reference's LCG fixture (common_helpers.rs:476-519): (q bytes, x f32)."""
     q = np.zeros(n_superblocks * Q4KM_SB_BYTES, np.uint8)

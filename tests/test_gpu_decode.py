@@ -1,0 +1,129 @@
+"""The fused-source matvec (x = a + b, unit RMS, (value, epoch) sources) and the decode sweep
+built from it, against the CPU oracle's sweep on small shapes."""
+import ctypes as C
+
+import numpy as np
+import pytest
+import torch
+
+import oracle
+from conftest import load_pkg
+
+pytestmark = pytest.mark.gpu
+NORMWISE_TOL = 1e-5
+
+
+def dev(a):
+    return torch.from_numpy(np.ascontiguousarray(a)).cuda()
+
+
+def fused(ffi, q, rows, n_sb, x=None, x2=None, xp=None, x2p=None, epoch=None, rms=False, gather=None, y=None, st=None):
+    xs = ffi.AxcXSrc(x.data_ptr() if x is not None else None, x2.data_ptr() if x2 is not None else None,
+                     xp.data_ptr() if xp is not None else None, x2p.data_ptr() if x2p is not None else None,
+                     epoch.data_ptr() if epoch is not None else None, 1 if rms else 0)
+    rc = ffi.lib().axc_cuda_q4k_matvec_fused(q.data_ptr(), C.byref(xs), y.data_ptr() if y is not None else None,
+                                             rows, n_sb, C.byref(gather) if gather is not None else None,
+                                             int(torch.cuda.current_stream().cuda_stream),
+                                             st.data_ptr() if st is not None else None, None)
+    return rc
+
+
+@pytest.mark.parametrize("rows,n_sb", [(33, 1), (257, 16), (64, 112), (1000, 32)])
+@pytest.mark.parametrize("second,rms", [(False, False), (True, False), (False, True), (True, True)])
+def test_fused_source_matches_oracle(ffi, ops, synth, rows, n_sb, second, rms):
+    q = synth.q4k_weights(rows, n_sb, 7000 + rows + n_sb)
+    a = synth.activations(n_sb * 256, 7100 + rows)
+    b = synth.activations(n_sb * 256, 7200 + rows)
+    x = (a + b).astype(np.float32) if second else a
+    x_eff = oracle.unit_rms(x) if rms else x
+    y_ref = oracle.matvec_rows("q4k", q, x_eff, rows, n_sb)
+    _y64, mag = oracle.matvec_rows_f64("q4k", q, x_eff, rows, n_sb)
+    y = torch.empty(rows, device="cuda")
+    st = ops.new_status()
+    assert fused(ffi, dev(q), rows, n_sb, x=dev(a), x2=dev(b) if second else None, rms=rms, y=y, st=st) == 0
+    torch.cuda.synchronize()
+    assert int(st.item()) == 0
+    assert (np.abs(y.cpu().numpy() - y_ref) / mag).max() <= NORMWISE_TOL
+
+
+def test_fused_source_reads_epoch_words_and_chains(ffi, ops, synth):
+    """Producer with the all-gather epilogue (world 1), consumer polling its words: g + u with
+    unit RMS straight from the (value, epoch) vector, no finish launch in between."""
+    coll = load_pkg("collective")
+    ffn, hid = 512, 256
+    gu_w = synth.q4k_weights(2 * ffn, hid // 256, 7301)
+    dn_w = synth.q4k_weights(hid, ffn // 256, 7302)
+    x = synth.activations(hid, 7303)
+    pg = coll.PeerGather(2 * ffn, 1, "cuda")
+    st = ops.new_status()
+    y = torch.empty(hid, device="cuda")
+    for it in range(2):
+        pg.begin_step()
+        pg.matvec(dev(gu_w), dev(x), hid // 256, 0, status=st)
+        pairs = pg.pairs
+        second = pairs[ffn:]
+        assert fused(ffi, dev(dn_w), hid, ffn // 256, xp=pairs, x2p=second, epoch=pg.epoch, rms=True, y=y, st=st) == 0
+        torch.cuda.synchronize()
+        assert int(st.item()) == 0
+        gu = oracle.matvec_rows("q4k", gu_w, x, 2 * ffn, hid // 256)
+        xin = oracle.unit_rms(gu[:ffn] + gu[ffn:])
+        y_ref = oracle.matvec_rows("q4k", dn_w, xin, hid, ffn // 256)
+        _y64, mag = oracle.matvec_rows_f64("q4k", dn_w, xin, hid, ffn // 256)
+        assert (np.abs(y.cpu().numpy() - y_ref) / mag).max() <= 2e-5   # two chained fast kernels
+
+
+def test_fused_source_times_out_on_missing_epoch(ffi, ops, synth):
+    """Words that never arrive: bounded wait, status bit 4, context stays usable."""
+    q = dev(synth.q4k_weights(8, 1, 7401))
+    pairs = torch.zeros(256, dtype=torch.int64, device="cuda")
+    epoch = torch.ones(1, dtype=torch.int32, device="cuda")
+    st = ops.new_status()
+    y = torch.empty(8, device="cuda")
+    assert fused(ffi, q, 8, 1, xp=pairs, epoch=epoch, y=y, st=st) == 0
+    torch.cuda.synchronize()
+    assert int(st.item()) & 4
+    assert torch.ones(3, device="cuda").sum().item() == 3.0
+
+
+def test_fused_source_argument_checks(ffi, ops, synth):
+    q = dev(synth.q4k_weights(8, 1, 7501))
+    x = dev(synth.activations(256, 7502))
+    y = torch.empty(8, device="cuda")
+    pairs = torch.zeros(256, dtype=torch.int64, device="cuda")
+    assert fused(ffi, q, 8, 1, y=y) == 100                         # no source
+    assert fused(ffi, q, 8, 1, x=x, xp=pairs, y=y) == 100          # two first sources
+    assert fused(ffi, q, 8, 1, xp=pairs, y=y) == 100               # epoch words without the counter
+    assert fused(ffi, q, 8, 1, x=x) == 100                         # nowhere to put y
+    assert fused(ffi, q, 8, 129, x=x, y=y) == 100                  # row too long for this kernel
+
+
+def test_decode_sweep_matches_oracle_on_a_small_stack():
+    decode = load_pkg("decode")
+    shape = decode.SweepShape(hidden=512, kv=128, ffn=1024, layers=3)
+    sweep = decode.DecodeSweep(shape, "cuda", seed=4242)
+    assert sweep.world == 1 and sweep.launches_per_token == 13
+    rng = np.random.default_rng(5)
+    h0 = rng.standard_normal(shape.hidden).astype(np.float32)
+    weights = [tuple(w.cpu().numpy() for w in layer) for layer in sweep.weights]
+    sweep.h.copy_(dev(h0))
+    sweep.token(normalise_input=False)
+    torch.cuda.synchronize()
+    assert int(sweep.status.item()) == 0
+    outs, d, h1, ksum = oracle.decode_token(weights, shape.hidden, shape.kv, shape.ffn, h0, normalise_input=False)
+    # first layer's first linear sees identical inputs: the per-kernel bar applies
+    _y64, mag = oracle.matvec_rows_f64("q4k", weights[0][0], h0, shape.hidden + 2 * shape.kv, shape.hidden // 256)
+    assert (np.abs(sweep.output(0, 0).cpu().numpy() - outs[0][0]) / mag).max() <= NORMWISE_TOL
+    # deeper vectors carry the rounding differences of every kernel before them
+    for layer in range(shape.layers):
+        for j in range(4):
+            got, ref = sweep.output(layer, j).cpu().numpy(), outs[layer][j]
+            assert np.abs(got - ref).max() <= 1e-3 * np.sqrt(np.mean(ref.astype(np.float64) ** 2)), (layer, j)
+    assert np.abs(sweep.hidden_out().cpu().numpy() - h1).max() <= 1e-3
+    assert abs(float(sweep.kv_checksum().item()) - ksum) <= 1e-3 * max(1.0, abs(ksum))
+    # second token: h = unitRMS(d) through the first launch's normalisation
+    sweep.advance()
+    sweep.token()
+    torch.cuda.synchronize()
+    outs2, d2, h2, _ = oracle.decode_token(weights, shape.hidden, shape.kv, shape.ffn, d, normalise_input=True)
+    assert np.abs(sweep.hidden_out().cpu().numpy() - h2).max() <= 2e-3
+    assert int(sweep.status.item()) == 0

@@ -177,3 +177,22 @@ def test_prefill_oracle_matches_numpy_gemm(synth):
     ab = torch.from_numpy(a.copy()).to(torch.bfloat16).to(torch.float64).numpy()
     ref = ab @ wb.T
     assert np.abs(c - ref).max() / np.abs(ref).max() < 1e-5
+
+
+def test_unit_rms_and_decode_token_shapes(synth):
+    v = np.arange(1, 9, dtype=np.float32)
+    u = oracle.unit_rms(v)
+    assert u.dtype == np.float32 and abs(float(np.mean(u.astype(np.float64) ** 2)) - 1.0) < 1e-6
+    hid, kv, ffn = 256, 64, 512
+    weights = [(synth.q4k_weights(hid + 2 * kv, 1, 10 + l), synth.q4k_weights(hid, 1, 20 + l),
+                synth.q4k_weights(2 * ffn, 1, 30 + l), synth.q4k_weights(hid, 2, 40 + l)) for l in range(2)]
+    h = synth.activations(hid, 50)
+    outs, d, h1, ksum = oracle.decode_token(weights, hid, kv, ffn, h, normalise_input=False)
+    assert [o.size for o in outs[0]] == [hid + 2 * kv, hid, 2 * ffn, hid] and len(outs) == 2
+    assert np.array_equal(d, outs[1][3]) and np.array_equal(h1, oracle.unit_rms(d))
+    # the first linear is the plain reference matvec on the raw h; the third sees unitRMS(o)
+    assert np.array_equal(outs[0][0], oracle.matvec_rows("q4k", weights[0][0], h, hid + 2 * kv, 1))
+    assert np.array_equal(outs[0][2], oracle.matvec_rows("q4k", weights[0][2], oracle.unit_rms(outs[0][1]), 2 * ffn, 1))
+    assert np.isfinite(ksum)
+    again = oracle.decode_token(weights, hid, kv, ffn, h, normalise_input=False)
+    assert np.array_equal(again[1], d)
