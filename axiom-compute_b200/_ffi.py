@@ -29,6 +29,7 @@ AXC_ERR_WORKGROUP_COUNT_EXCEEDS_LIMIT = 20
 AXC_ERR_STAGING_COPY_FAILED = 25
 AXC_ERR_INVALID_ARGUMENT = 100
 
+AXC_FINISH_OVERLAP_PREVIOUS = 1
 AXC_TY_OTHER, AXC_TY_U8, AXC_TY_F32, AXC_TY_U32 = 0, 1, 2, 3
 AXC_ACCESS_READ_ONLY, AXC_ACCESS_READ_WRITE, AXC_ACCESS_WRITE_ONLY = 1, 2, 3
 
@@ -120,7 +121,7 @@ SYMBOLS = {
     "axc_cuda_q4k_matvec_fused": (C.c_int, [_VP, C.POINTER(AxcXSrc), _VP, C.c_uint32, C.c_uint32,
                                             C.POINTER(AxcGather), _VP, _VP, C.POINTER(AxcTuning)]),
     "axc_cuda_gather_next_epoch": (C.c_int, [_VP, _VP]),
-    "axc_cuda_gather_finish": (C.c_int, [_VP, _VP, _VP, C.c_uint32, _VP, _VP]),
+    "axc_cuda_gather_finish": (C.c_int, [_VP, _VP, _VP, C.c_uint32, _VP, _VP, C.c_uint32]),
     "axc_cuda_q4k_matvec_static": (C.c_int, [_VP, _VP, _VP, C.c_uint32, C.c_uint32, _VP]),
     "axc_cuda_version": (C.c_int, []),
 }

@@ -83,5 +83,5 @@ class PeerGather:
         with torch.cuda.device(self.device):
             rc = _ffi.lib().axc_cuda_gather_finish(
                 self.pairs.data_ptr(), self.epoch.data_ptr(), self.values.data_ptr(), n, self._stream(),
-                status.data_ptr() if status is not None else None)
+                status.data_ptr() if status is not None else None, 0)
         _raise_for(rc)

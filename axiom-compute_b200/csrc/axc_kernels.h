@@ -61,7 +61,7 @@ cudaError_t launch_q4k_dequant(const uint8_t* q, float* w, uint32_t rows, uint32
                                cudaStream_t stream);
 
 cudaError_t launch_gather_finish(const uint64_t* pairs, const uint32_t* epoch_ptr, float* out, uint32_t n,
-                                 uint32_t* status, cudaStream_t stream);
+                                 uint32_t* status, cudaStream_t stream, bool overlap);
 cudaError_t launch_gather_next_epoch(uint32_t* epoch_ptr, cudaStream_t stream);
 
 // Quantised form of x for `n_pos` 64-column positions (see q4_stream.cu): bytes needed and the

@@ -821,12 +821,12 @@ int axc_cuda_gather_next_epoch(uint32_t* epoch, void* stream) {
 }
 
 int axc_cuda_gather_finish(const uint64_t* pairs, const uint32_t* epoch, float* out, uint32_t n,
-                           void* stream, uint32_t* status) {
+                           void* stream, uint32_t* status, uint32_t flags) {
     clear_error();
     if (n == 0) return AXC_OK;
     if (!pairs || !epoch || !out || ((uintptr_t)pairs & 7u))
         return fail(AXC_ERR_INVALID_ARGUMENT, "null or misaligned pair storage / epoch / output");
-    return launch_result(axc::launch_gather_finish(pairs, epoch, out, n, status, (cudaStream_t)stream));
+    return launch_result(axc::launch_gather_finish(pairs, epoch, out, n, status, (cudaStream_t)stream, (flags & AXC_FINISH_OVERLAP_PREVIOUS) != 0));
 }
 
 int axc_cuda_q4k_matvec_plan(uint32_t rows, uint32_t n_superblocks, const axc_tuning* tuning,

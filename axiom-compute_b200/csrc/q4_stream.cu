@@ -251,9 +251,9 @@ __device__ __forceinline__ float warp_reduce_transposed(const float (&v)[PASSES]
 // xs[k][pos] with an XOR swizzle so that these stores and the per-thread reads of the matvec
 // are free of shared-memory bank conflicts; xm[pos] = (sum of columns 0..31, sum of columns
 // 32..63, two factors of 2^(e-21)).  `nthreads` is a multiple of 32; all threads must call.
-// `load4(i)` returns columns 4i..4i+3.  Returns this thread's share of sum(x^2).
-template <class Load4>
-__device__ __forceinline__ float quantize_x_positions_from(Load4 load4, uint4* xs, float4* xm,
+// `load16(i, v)` fills v[0..3] with columns 4i..4i+15.  Returns this thread's share of sum(x^2).
+template <class Load16>
+__device__ __forceinline__ float quantize_x_positions_from(Load16 load16, uint4* xs, float4* xm,
                                                            uint32_t n_pos, uint32_t pos_end, uint32_t pitch,
                                                            uint32_t tid, uint32_t nthreads) {
     float sumsq = 0.0f;
@@ -263,9 +263,12 @@ __device__ __forceinline__ float quantize_x_positions_from(Load4 load4, uint4* x
         for (uint32_t pos = tid >> 2; pos < pos_end; pos += nthreads >> 2) {
             const bool valid = pos < n_pos;
             float4 v[4];
+            if (valid) {
+                load16(pos * 16 + qt * 4, v);
+            } else {
 #pragma unroll
-            for (int u = 0; u < 4; ++u)
-                v[u] = valid ? load4(pos * 16 + qt * 4 + u) : make_float4(0.f, 0.f, 0.f, 0.f);
+                for (int u = 0; u < 4; ++u) v[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+            }
             // largest finite |x| of the chunk (NaNs are ignored by fmaxf) and the half sums
             float m = 0.0f, s = 0.0f;
 #pragma unroll
@@ -304,23 +307,32 @@ __device__ __forceinline__ void quantize_x_positions(const float* __restrict__ x
                                                      uint32_t n_pos, uint32_t pos_end, uint32_t pitch,
                                                      uint32_t tid, uint32_t nthreads) {
     const float4* xg = reinterpret_cast<const float4*>(x);
-    (void)quantize_x_positions_from([&](uint32_t i) { return __ldg(xg + i); }, xs, xm, n_pos, pos_end, pitch,
-                                    tid, nthreads);
+    (void)quantize_x_positions_from(
+        [&](uint32_t i, float4* v) {
+#pragma unroll
+            for (int u = 0; u < 4; ++u) v[u] = __ldg(xg + i + u);
+        },
+        xs, xm, n_pos, pos_end, pitch, tid, nthreads);
 }
 
-// Four columns of a (value, epoch) vector: polls (bypassing L1) until all four words carry an
-// epoch >= `epoch`.  Bounded; after one timeout the thread only looks once at later words.
-__device__ __forceinline__ float4 load_pairs4(const uint64_t* base, uint32_t i, uint32_t epoch, bool& gave_up) {
+// Sixteen columns (4i .. 4i+15) of a (value, epoch) vector.  All eight 16-byte loads are issued
+// together (bypassing L1) and the epochs checked afterwards; only if a word is still old does the
+// thread poll, bounded, until all sixteen carry an epoch >= `epoch`.  After one timeout the
+// thread only looks once at later words.
+__device__ __forceinline__ void load_pairs16(const uint64_t* base, uint32_t i, uint32_t epoch, bool& gave_up,
+                                             float4* v) {
     const uint4* src = reinterpret_cast<const uint4*>(base) + 2 * (size_t)i;
-    uint4 a, b;
+    uint4 w[8];
     uint32_t it = gave_up ? (1u << 20) - 1u : 0u;
     for (;;) {
-        asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];"
-                     : "=r"(a.x), "=r"(a.y), "=r"(a.z), "=r"(a.w) : "l"(src) : "memory");
-        asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];"
-                     : "=r"(b.x), "=r"(b.y), "=r"(b.z), "=r"(b.w) : "l"(src + 1) : "memory");
-        const bool ok = (int32_t)(a.y - epoch) >= 0 && (int32_t)(a.w - epoch) >= 0 &&
-                        (int32_t)(b.y - epoch) >= 0 && (int32_t)(b.w - epoch) >= 0;
+#pragma unroll
+        for (int u = 0; u < 8; ++u)
+            asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];"
+                         : "=r"(w[u].x), "=r"(w[u].y), "=r"(w[u].z), "=r"(w[u].w) : "l"(src + u) : "memory");
+        bool ok = true;
+#pragma unroll
+        for (int u = 0; u < 8; ++u)
+            ok = ok && (int32_t)(w[u].y - epoch) >= 0 && (int32_t)(w[u].w - epoch) >= 0;
         if (ok) break;
         if (++it >= (1u << 20)) {
             gave_up = true;
@@ -328,7 +340,10 @@ __device__ __forceinline__ float4 load_pairs4(const uint64_t* base, uint32_t i, 
         }
         __nanosleep(64);
     }
-    return make_float4(__uint_as_float(a.x), __uint_as_float(a.z), __uint_as_float(b.x), __uint_as_float(b.z));
+#pragma unroll
+    for (int u = 0; u < 4; ++u)
+        v[u] = make_float4(__uint_as_float(w[2 * u].x), __uint_as_float(w[2 * u].z),
+                           __uint_as_float(w[2 * u + 1].x), __uint_as_float(w[2 * u + 1].z));
 }
 
 template <int FMT, int PASSES, bool PREPARED, bool GATHER, bool XFUSE>
@@ -434,13 +449,25 @@ __global__ void __launch_bounds__(512, 1) q4_matvec_stream_kernel(const StreamPa
         const float4* xa = reinterpret_cast<const float4*>(p.x);
         const float4* xb = reinterpret_cast<const float4*>(p.x2);
         float sq = quantize_x_positions_from(
-            [&](uint32_t i) {
-                float4 v = p.x_pairs ? load_pairs4(p.x_pairs, i, x_epoch, gave_up) : __ldg(xa + i);
-                if (p.x2_pairs || xb) {
-                    const float4 w = p.x2_pairs ? load_pairs4(p.x2_pairs, i, x_epoch, gave_up) : __ldg(xb + i);
-                    v.x += w.x, v.y += w.y, v.z += w.z, v.w += w.w;
+            [&](uint32_t i, float4* v) {
+                if (p.x_pairs) {
+                    load_pairs16(p.x_pairs, i, x_epoch, gave_up, v);
+                } else {
+#pragma unroll
+                    for (int u = 0; u < 4; ++u) v[u] = __ldg(xa + i + u);
                 }
-                return v;
+                if (p.x2_pairs || xb) {
+                    float4 w[4];
+                    if (p.x2_pairs) {
+                        load_pairs16(p.x2_pairs, i, x_epoch, gave_up, w);
+                    } else {
+#pragma unroll
+                        for (int u = 0; u < 4; ++u) w[u] = __ldg(xb + i + u);
+                    }
+#pragma unroll
+                    for (int u = 0; u < 4; ++u)
+                        v[u].x += w[u].x, v[u].y += w[u].y, v[u].z += w[u].z, v[u].w += w[u].w;
+                }
             },
             xs, xm, p.n_pos, p.x_pos_end, p.x_pitch, tid, blockDim.x);
         if (gave_up && p.status) atomicOr(p.status, ERR_PEER_WAIT_TIMEOUT);
@@ -732,9 +759,14 @@ static cudaError_t launch_stream(const uint8_t* q, const float* x, float* y, uin
 // Consumer side of the fused all-gather: waits until every (value, epoch) word of `pairs` carries
 // the current epoch and writes the values out as a plain fp32 vector.  Bounded (about two seconds
 // per element that never arrives), then ERR_PEER_WAIT_TIMEOUT and the stale value is written.
+// With `overlap` the kernel does not wait for the launch before it (whose words it polls for
+// anyway): the caller guarantees that launch neither advances the epoch nor touches `out`.
 __global__ void gather_finish_kernel(const uint64_t* __restrict__ pairs, const uint32_t* __restrict__ epoch_ptr,
-                                     float* __restrict__ out, uint32_t n, uint32_t* status) {
-    const uint32_t epoch = *epoch_ptr;
+                                     float* __restrict__ out, uint32_t n, uint32_t* status, uint32_t overlap) {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    if (!overlap) asm volatile("griddepcontrol.wait;" ::: "memory");
+    uint32_t epoch;
+    asm volatile("ld.relaxed.gpu.global.u32 %0, [%1];" : "=r"(epoch) : "l"(epoch_ptr) : "memory");
     bool gave_up = false;
     for (uint32_t i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) {
         uint64_t w = 0;
@@ -755,12 +787,17 @@ __global__ void gather_finish_kernel(const uint64_t* __restrict__ pairs, const u
 __global__ void gather_next_epoch_kernel(uint32_t* epoch_ptr) { *epoch_ptr += 1; }
 
 cudaError_t launch_gather_finish(const uint64_t* pairs, const uint32_t* epoch_ptr, float* out, uint32_t n,
-                                 uint32_t* status, cudaStream_t stream) {
+                                 uint32_t* status, cudaStream_t stream, bool overlap) {
     if (n == 0) return cudaSuccess;
     uint32_t blocks = (n + 255) / 256;
     if (blocks > 592) blocks = 592;
-    gather_finish_kernel<<<blocks, 256, 0, stream>>>(pairs, epoch_ptr, out, n, status);
-    return cudaGetLastError();
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(blocks), cfg.blockDim = dim3(256), cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr, cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, gather_finish_kernel, pairs, epoch_ptr, out, n, status, overlap ? 1u : 0u);
 }
 
 cudaError_t launch_gather_next_epoch(uint32_t* epoch_ptr, cudaStream_t stream) {

@@ -12,8 +12,11 @@ token's pass through ``layers`` blocks of seven linears with the dataflow
 Every elementwise step is folded into the matvec that consumes it (``axc_cuda_q4k_matvec_fused``:
 x = a [+ b], unit RMS as one output scale), Wq/Wk/Wv and Wgate/Wup are stored as one matrix each,
 so a layer is four launches.  With more than one GPU every linear is row-sharded and its
-all-gather is fused into the producing kernel's epilogue; the consuming kernel polls the
-(value, epoch) words itself, so there is no collective launch between dependent linears.
+all-gather is fused into the producing kernel's epilogue.  Between dependent linears a small
+finish kernel (started while the producer is still running) waits for the (value, epoch) words
+and unpacks them once into a plain vector that every CTA of the consumer then reads through L1;
+``consumer_polls=True`` lets every consumer CTA poll the words itself instead (no launch in
+between, but 2 x the bytes per CTA past L1: measured slower).
 
 Weights are synthetic (uniform nibbles and scale bytes, d and dmin = f16(|N(0,1)| * 0.01)),
 generated on the device in eight row chunks per linear so that the global matrices are the same
@@ -76,8 +79,10 @@ def synth_chunk(rows: int, n_sb: int, seed: int, device) -> torch.Tensor:
 class DecodeSweep:
     """One rank's share of the stack plus the buffers and launches of a token."""
 
-    def __init__(self, shape: SweepShape, device, seed: int = 0xA0C0 + 4 * 16, group=None, tuning=None):
+    def __init__(self, shape: SweepShape, device, seed: int = 0xA0C0 + 4 * 16, group=None, tuning=None,
+                 consumer_polls: bool = False):
         self.shape, self.device = shape, torch.device(device)
+        self.consumer_polls = bool(consumer_polls)
         self.world, self.rank = 1, 0
         self.tuning = tuning
         dist_on = group is not None or (torch.distributed.is_available() and torch.distributed.is_initialized()
@@ -125,11 +130,15 @@ class DecodeSweep:
             torch.cuda.synchronize(self.device)
             dist.barrier(group)
             self.ptr_table = torch.tensor(ptrs, dtype=torch.int64, device=self.device)
-            self.vec = None
         else:
             self.pairs = None
-            self.vec = torch.zeros(words, dtype=torch.float32, device=self.device)
-        self.launches_per_token = 4 * shape.layers + (3 if self.world > 1 else 1)
+        self.vec = torch.zeros(words, dtype=torch.float32, device=self.device)
+        if self.world == 1:
+            self.launches_per_token = 4 * shape.layers + 1
+        elif self.consumer_polls:
+            self.launches_per_token = 4 * shape.layers + 3
+        else:
+            self.launches_per_token = 8 * shape.layers + 2
 
     # -- helpers ---------------------------------------------------------------------------
     def _stream(self) -> int:
@@ -147,6 +156,10 @@ class DecodeSweep:
                                self.rank * rows_local)
             rc = _ffi.lib().axc_cuda_q4k_matvec_fused(w.data_ptr(), C.byref(xsrc), None, rows_local, k // 256,
                                                       C.byref(g), self._stream(), st, tn)
+            if rc == 0 and not self.consumer_polls:
+                rc = _ffi.lib().axc_cuda_gather_finish(
+                    self.pairs.data_ptr() + off * 8, self.epoch.data_ptr(), self.vec.data_ptr() + off * 4, rows,
+                    self._stream(), st, _ffi.AXC_FINISH_OVERLAP_PREVIOUS)
         else:
             rc = _ffi.lib().axc_cuda_q4k_matvec_fused(w.data_ptr(), C.byref(xsrc), self.vec.data_ptr() + off * 4,
                                                       rows_local, k // 256, None, self._stream(), st, tn)
@@ -155,7 +168,7 @@ class DecodeSweep:
     def _src(self, layer: int, j: int, word: int = 0, second: Optional[int] = None, rms: bool = True):
         """x source = output of linear j of `layer` starting at `word` (+ the vector at `second`)."""
         base = self.offsets[layer][j] + word
-        if self.world > 1:
+        if self.world > 1 and self.consumer_polls:
             p = self.pairs.data_ptr()
             return _ffi.AxcXSrc(None, None, p + base * 8,
                                 None if second is None else p + (self.offsets[layer][j] + second) * 8,
@@ -183,21 +196,14 @@ class DecodeSweep:
                 self._linear(layer, 2, self._src(layer, 1))             # g, u
                 self._linear(layer, 3, self._src(layer, 2, 0, sh.ffn))  # d = Wdown . unitRMS(g + u)
             last = self.offsets[sh.layers - 1][3]
-            if self.world > 1:
+            if self.world > 1 and self.consumer_polls:
+                # nothing unpacked the words yet: every vector (k and v included) in one pass
                 _raise_for(_ffi.lib().axc_cuda_gather_finish(
-                    self.pairs.data_ptr() + last * 8, self.epoch.data_ptr(), self.d_last.data_ptr(), sh.hidden,
-                    self._stream(), self.status.data_ptr()))
-                # k and v of every layer must also be complete on this rank before they are read
-                _raise_for(_ffi.lib().axc_cuda_gather_finish(
-                    self.pairs.data_ptr(), self.epoch.data_ptr(), self._plain_store().data_ptr(),
-                    sh.vector_words_per_layer * sh.layers, self._stream(), self.status.data_ptr()))
-            else:
-                self.d_last.copy_(self.vec[last:last + sh.hidden])
+                    self.pairs.data_ptr(), self.epoch.data_ptr(), self.vec.data_ptr(),
+                    sh.vector_words_per_layer * sh.layers, self._stream(), self.status.data_ptr(), 0))
+            self.d_last.copy_(self.vec[last:last + sh.hidden])
 
     def _plain_store(self) -> torch.Tensor:
-        if self.vec is None:
-            self.vec = torch.zeros(self.shape.vector_words_per_layer * self.shape.layers, dtype=torch.float32,
-                                   device=self.device)
         return self.vec
 
     def advance(self) -> None:

@@ -281,9 +281,13 @@ int axc_cuda_q4k_matvec_fused(const void* q, const axc_xsrc* xs, float* y, uint3
                               uint32_t* status, const axc_tuning* tuning);
 /* *epoch += 1, in stream order (a one-thread kernel). */
 int axc_cuda_gather_next_epoch(uint32_t* epoch, void* stream);
-/* Consumer side: pairs = this rank's own pair storage (n words), out = n fp32 values. */
+/* Consumer side: pairs = this rank's own pair storage (n words), out = n fp32 values.
+ * flags: AXC_FINISH_OVERLAP_PREVIOUS lets the kernel start before the launch directly before it
+ * in the stream has completed (it polls for that launch's words anyway); the caller guarantees
+ * that launch neither advances the epoch nor reads or writes `out`. */
+#define AXC_FINISH_OVERLAP_PREVIOUS 1u
 int axc_cuda_gather_finish(const uint64_t* pairs, const uint32_t* epoch, float* out, uint32_t n,
-                           void* stream, uint32_t* status);
+                           void* stream, uint32_t* status, uint32_t flags);
 
 /* Launch geometry the matvec launchers would use (no launch). */
 int axc_cuda_q4k_matvec_plan(uint32_t rows, uint32_t n_superblocks, const axc_tuning* tuning,

@@ -97,6 +97,28 @@ def test_fused_source_argument_checks(ffi, ops, synth):
     assert fused(ffi, q, 8, 129, x=x, y=y) == 100                  # row too long for this kernel
 
 
+def test_gather_finish_overlapping_its_producer(ffi, ops, synth):
+    """finish launched with the overlap flag right behind its producer: it starts early, polls
+    for the producer's words and delivers exactly the plain kernel's values."""
+    coll = load_pkg("collective")
+    rows, n_sb = 3000, 16
+    q, x = dev(synth.q4k_weights(rows, n_sb, 7601)), dev(synth.activations(n_sb * 256, 7602))
+    pg = coll.PeerGather(rows, 1, "cuda")
+    st = ops.new_status()
+    out = torch.zeros(rows, device="cuda")
+    for it in range(3):
+        pg.begin_step()
+        pg.matvec(q, x, n_sb, 0, status=st)
+        rc = ffi.lib().axc_cuda_gather_finish(pg.pairs.data_ptr(), pg.epoch.data_ptr(), out.data_ptr(), rows,
+                                              int(torch.cuda.current_stream().cuda_stream), st.data_ptr(),
+                                              ffi.AXC_FINISH_OVERLAP_PREVIOUS)
+        assert rc == 0
+        y = ops.q4k_matvec(q, x, rows, n_sb)
+        assert torch.equal(out, y)
+        out.zero_()
+    assert int(st.item()) == 0
+
+
 def test_decode_sweep_matches_oracle_on_a_small_stack():
     decode = load_pkg("decode")
     shape = decode.SweepShape(hidden=512, kv=128, ffn=1024, layers=3)
