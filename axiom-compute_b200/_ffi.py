@@ -118,6 +118,7 @@ SYMBOLS = {
                                            C.POINTER(C.c_int32)]),
     "axc_cuda_q4k_matvec_allgather": (C.c_int, [_VP, _VP, C.c_uint32, C.c_uint32, C.POINTER(AxcGather), _VP, _VP,
                                                 C.POINTER(AxcTuning)]),
+    "axc_cuda_q4k_prefill": (C.c_int, [_VP, _VP, _VP, C.c_uint32, C.c_uint32, C.c_uint32, _VP, _VP]),
     "axc_cuda_q4k_matvec_fused": (C.c_int, [_VP, C.POINTER(AxcXSrc), _VP, C.c_uint32, C.c_uint32,
                                             C.POINTER(AxcGather), _VP, _VP, C.POINTER(AxcTuning)]),
     "axc_cuda_gather_next_epoch": (C.c_int, [_VP, _VP]),

@@ -14,7 +14,7 @@ import sys
 PKG_DIR = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(PKG_DIR, "csrc")
 LIB_PATH = os.path.join(PKG_DIR, "libaxc_cuda.so")
-SOURCES = ["axc_runtime.cu", "q4_stream.cu", "q4k_matvec.cu", "q4_0_matvec.cu", "axc_static.cu"]
+SOURCES = ["axc_runtime.cu", "q4_stream.cu", "q4k_matvec.cu", "q4_0_matvec.cu", "q4k_prefill.cu", "axc_static.cu"]
 HEADERS = ["axc_device.cuh", "axc_kernels.h", os.path.join("..", "..", "include", "axc_cuda.h")]
 
 NVCC_FLAGS = [

@@ -783,6 +783,23 @@ int axc_cuda_q4k_matvec_allgather(const void* q, const float* x, uint32_t rows_l
     return launch_result(axc::launch_q4k_matvec((const uint8_t*)q, x, nullptr, rows_local, n_superblocks, status, (cudaStream_t)stream, t, sm_count_of_current_device(), nullptr));
 }
 
+int axc_cuda_q4k_prefill(const void* q, const uint16_t* a_bf16, float* c, uint32_t m_tokens,
+                         uint32_t n_rows, uint32_t n_superblocks, void* stream, uint32_t* status) {
+    clear_error();
+    if (m_tokens == 0 || n_rows == 0) return AXC_OK;
+    if (n_superblocks == 0) return fail(AXC_ERR_INVALID_ARGUMENT, "prefill needs at least one superblock per row");
+    int rc = check_dev_ptrs(q, a_bf16, c);
+    if (rc != AXC_OK) return rc;
+    if ((uint64_t)n_superblocks * 144u >= (1ull << 32) || (uint64_t)m_tokens * n_rows >= (1ull << 40))
+        return fail(AXC_ERR_INVALID_ARGUMENT, "prefill shape out of range");
+    cudaError_t e = axc::launch_q4k_prefill((const uint8_t*)q, a_bf16, c, m_tokens, n_rows, n_superblocks, status, (cudaStream_t)stream);
+    if (e == cudaErrorNotSupported)
+        return fail(AXC_ERR_PIPELINE_CREATION_FAILED, "pipeline creation failed: the driver does not provide cuTensorMapEncodeTiled");
+    if (e == cudaErrorInvalidValue)
+        return fail(AXC_ERR_INVALID_ARGUMENT, "tensor map rejected (pointer alignment or shape)");
+    return launch_result(e);
+}
+
 int axc_cuda_q4k_matvec_fused(const void* q, const axc_xsrc* xs, float* y, uint32_t rows,
                               uint32_t n_superblocks, const axc_gather* g, void* stream,
                               uint32_t* status, const axc_tuning* tuning) {

@@ -260,6 +260,19 @@ typedef struct axc_gather {
 int axc_cuda_q4k_matvec_allgather(const void* q, const float* x, uint32_t rows_local,
                                   uint32_t n_superblocks, const axc_gather* g, void* stream,
                                   uint32_t* status, const axc_tuning* tuning);
+/* Batched prefill (M > 1), the one place where the path is a dense contraction and runs on the
+ * tensor cores (tcgen05, accumulators in tensor memory):
+ *   C[m][n] = sum_k A[m][k] * bf16(W[n][k]),  fp32 accumulate,
+ * A = m_tokens x (n_superblocks * 256) bf16 (row-major, as uint16 bit patterns), W = n_rows rows
+ * of n_superblocks Q4_K_M superblocks (the matvec's q layout), C = m_tokens x n_rows fp32
+ * row-major.  bf16(W) is the reference's fp32 dequantised weight (same operations and rounding
+ * points as examples/q4km_dequant_matvec.axc:91-112) rounded to nearest even.  All pointers are
+ * 16-byte aligned device memory.  The reference has no M > 1 kernel; the comparison is its CPU
+ * dequantisation followed by a GEMM (tolerance 1e-2 relative).  *status receives bit 0 if a
+ * bounded wait inside the kernel ran out. */
+int axc_cuda_q4k_prefill(const void* q, const uint16_t* a_bf16, float* c, uint32_t m_tokens,
+                         uint32_t n_rows, uint32_t n_superblocks, void* stream, uint32_t* status);
+
 /* Q4_K_M matvec whose activations are assembled inside the kernel: x = a [+ b], where a and b
  * are each a plain fp32 vector (x, x2) or a vector of (value, epoch) words that the all-gather
  * epilogue of an earlier call wrote (x_pairs, x2_pairs: the kernel itself polls, bounded, until
