@@ -573,9 +573,89 @@ def run_decode(args):
     print(json.dumps(line), flush=True)
 
 
+def run_prefill(args):
+    """`--workload prefill`: the batched-prefill contraction (M = 512 tokens, K = 4096, N = 14336;
+    tensor-pipe bound).  One step = one pass over 8 distinct weight matrices.  Single GPU."""
+    import torch
+    if int(os.environ.get("RANK", "0")) != 0:
+        return
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py: no CUDA device; this backend has no CPU path")
+    dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
+    torch.cuda.set_device(dev)
+    pkg = importlib.import_module("axiom-compute_b200")
+    ops = importlib.import_module("axiom-compute_b200.ops")
+    synth = pkg.synth
+    m, n, n_sb, n_mat = 512, ROWS, N_SB, 8
+    base = synth.q4k_weights(n, n_sb, synth.config_seed(3, 0))
+    rng = np.random.default_rng(synth.config_seed(3, 1))
+    a32 = rng.standard_normal((m, n_sb * 256)).astype(np.float32)
+    a_bf = torch.from_numpy(a32).to(torch.bfloat16)
+    a_dev = a_bf.to(dev)
+    weights = []
+    for j in range(n_mat):
+        w = np.roll(base.reshape(n, -1), 131 * j, axis=0).copy() if j else base
+        weights.append(torch.from_numpy(np.ascontiguousarray(w).reshape(-1)).to(dev))
+    outs = [torch.empty((m, n), dtype=torch.float32, device=dev) for _ in range(n_mat)]
+    status = ops.new_status(dev)
+
+    def step():
+        for j in range(n_mat):
+            ops.q4k_prefill(weights[j], a_dev, m, n, n_sb, c=outs[j], status=status)
+
+    step()
+    torch.cuda.synchronize()
+    if int(status.item()) != 0:
+        raise SystemExit(f"kernel status {int(status.item())}")
+    import oracle   # checker only: a few weight rows against dequant-then-GEMM on the CPU
+    rows = np.array([0, 127, 128, 9999, n - 1])
+    ref = oracle.q4km_prefill(np.ascontiguousarray(base.reshape(n, -1)[rows]).reshape(-1),
+                              a_bf.to(torch.float32).numpy(), m, len(rows), n_sb)
+    got = outs[0][:, torch.from_numpy(rows).to(dev)].cpu().numpy()
+    rms = float(np.sqrt(np.mean(ref.astype(np.float64) ** 2)))
+    if not (np.abs(got - ref) <= 1e-2 * np.maximum(np.abs(ref), rms)).all():
+        raise SystemExit("parity check failed before timing")
+    steps, warmup = max(1, min(args.steps, 500)), max(3, min(args.warmup, 20))
+    for _ in range(warmup):
+        step()
+    torch.cuda.synchronize()
+    sampler = ClockSampler(dev.index)
+    sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        step()
+    e1.record()
+    torch.cuda.synchronize()
+    sampler.stop()
+    ms = e0.elapsed_time(e1) / steps
+    flops = 2.0 * m * n * n_sb * 256
+    tf = flops * n_mat / (ms * 1e-3) / 1e12
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            pk = json.load(f)
+        peak, peak_src = float(pk["bf16_tflops"]), "measured (MEASURED_PEAKS.json bf16_tflops, burst)"
+    except Exception:
+        peak, peak_src = 1590.0, "fallback (1.59 PFLOP/s, earlier measurement on this pool)"
+    line = {
+        "metric": "q4k_prefill_512x4096x14336_tflops", "value": round(tf, 2), "unit": "TFLOP/s", "n_gpus": 1,
+        "steps": steps, "warmup": warmup, "ms_per_step": round(ms, 5), "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": "Q4_K_M batched prefill, M=512 tokens, K=4096, N=14336, bf16 operands, fp32 accumulate",
+                   "calls_per_step": n_mat, "launch": "stream",
+                   "l2": f"{n_mat} distinct weight matrices and outputs per step (0.5 GB) visited round-robin"},
+        "us_per_call": round(ms * 1e3 / n_mat, 3),
+        "roofline": {"bound": "tensor", "achieved": round(tf, 2), "peak": peak, "unit": "TFLOP/s",
+                     "frac": round(tf / peak, 4), "traffic": None, "kernel": "q4k_prefill_kernel",
+                     "flops_per_launch": flops, "peak_source": peak_src},
+        "cpu_baseline": None, "e2e": None, "gpu_launches": steps * n_mat, "clocks": sampler.summary(),
+    }
+    print(json.dumps(line), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--workload", choices=["matvec", "decode70b"], default="matvec",
+    ap.add_argument("--workload", choices=["matvec", "decode70b", "prefill"], default="matvec",
                     help="matvec: the headline 14336 x 4096 metric; decode70b: the 70B-shaped decode sweep")
     ap.add_argument("--layers", type=int, default=80, help="decode70b: layers in the stack")
     ap.add_argument("--gpus", type=int, default=1)
@@ -595,6 +675,8 @@ def main():
         run_reference(args)
     elif args.workload == "decode70b":
         run_decode(args)
+    elif args.workload == "prefill":
+        run_prefill(args)
     else:
         run_ours(args)
 
