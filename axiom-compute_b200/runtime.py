@@ -444,6 +444,13 @@ class CudaContext:
                                            st.rows_effective, st.blocks_per_row)
         return out_bufs
 
+    def bind(self, handle: KernelHandle, workgroups, inputs, output_sizes, push_constants) -> "BoundDispatch":
+        """``dispatch_handle`` with its arguments marshalled once: ``run()`` repeats the same
+        dispatch (same host input buffers, read again on every run; outputs land in the same
+        reusable bytearrays).  A Rust caller pays nothing for marshalling; this gives a Python
+        caller the same per-call cost (one foreign call)."""
+        return BoundDispatch(self, handle, workgroups, inputs, output_sizes, push_constants)
+
     def dispatch(self, req: DispatchRequest):
         """dispatch.rs:109-132: validate, prepare, dispatch once, drop the handle."""
         (in_ptrs, in_lens, n_in, out_ptrs, out_lens, n_out, pc_buf, pc_len, out_bufs,
@@ -488,6 +495,26 @@ class CudaContext:
             self.drop()
         except Exception:
             pass
+
+
+class BoundDispatch:
+    """One dispatch whose C arguments are built once (see ``CudaContext.bind``)."""
+
+    def __init__(self, ctx: CudaContext, handle: KernelHandle, workgroups, inputs, output_sizes, push_constants):
+        self._ctx, self._handle = ctx, handle
+        (self._in_ptrs, self._in_lens, self._n_in, self._out_ptrs, self._out_lens, self._n_out, self._pc_buf,
+         self._pc_len, self.outputs, self._keep) = CudaContext._marshal(inputs, output_sizes, push_constants)
+        self._wg = (C.c_uint32 * 3)(*[int(v) for v in workgroups])
+        self._pc_ptr = C.cast(self._pc_buf, C.c_void_p)
+        self._fn = _ffi.lib().axc_cuda_dispatch
+
+    def run(self):
+        """Dispatch once; returns the (reused) output buffers, one per binding."""
+        rc = self._fn(self._ctx._ptr, self._handle._ptr, self._wg, self._in_ptrs, self._in_lens, self._n_in,
+                      self._out_ptrs, self._out_lens, self._n_out, self._pc_ptr, self._pc_len, None)
+        if rc:
+            _raise_for(rc)
+        return self.outputs
 
 
 VulkanContext = CudaContext

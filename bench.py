@@ -432,13 +432,14 @@ def run_e2e(pkg, device_index, weights, x_host, rows_local, args, world, dist, d
         ctx.dispatch_handle(h, (rows_local, 1, 1), [weights[m].cpu().numpy(), x_host, b""],
                             [0, 0, rows_local * 4], pc)
         handles.append(h)
-    x_bytes = x_host.tobytes()
+    x_buf = bytearray(x_host.tobytes())   # the caller's host buffer: read again on every dispatch
     y_full = torch.empty(rows_local * world, dtype=torch.float32, device=dev) if world > 1 else None
+    bound = [ctx.bind(handles[m], (rows_local, 1, 1), [b"", x_buf, b""], [0, 0, rows_local * 4], pc)
+             for m in range(N_MATRICES)]
 
     def step():
         for m in range(N_MATRICES):
-            out = ctx.dispatch_handle(handles[m], (rows_local, 1, 1), [b"", x_bytes, b""],
-                                      [0, 0, rows_local * 4], pc)
+            out = bound[m].run()
             if world > 1:
                 y_loc = torch.frombuffer(out[2], dtype=torch.float32).to(dev, non_blocking=True)
                 dist.all_gather_into_tensor(y_full, y_loc)

@@ -250,3 +250,25 @@ def test_bench_dispatch_median_rule(axc, ctx):
     assert all(s > 0 for s in samples) and all(d > 0 for d in dev_ns)
     cpu = float(oracle.q4km_dequant_matvec_cpu(q, x, n))
     assert rel_err(float(f32(out[2])[0]), cpu) < 1e-5
+
+
+def test_bound_dispatch_repeats_and_rereads_host_input(axc, ctx, synth):
+    """``bind`` marshals once; every ``run`` re-reads the caller's host buffer and reuses the
+    output buffers."""
+    rows, n = 40, 4
+    q = synth.q4k_weights(rows, n, 8801)
+    x = synth.activations(n * 256, 8802)
+    plan = axc.q4_matvec_binding_plan("q4km_dequant_matvec")
+    h = ctx.prepare_kernel(SPIRV_STANDIN + [88], plan, 4, "q4km_dequant_matvec")
+    xbuf = bytearray(x.tobytes())
+    b = ctx.bind(h, (rows, 1, 1), [q, xbuf, b""], [0, 0, rows * 4], pc(n))
+    out1 = f32(b.run()[2]).copy()
+    y_ref = oracle.matvec_rows("q4k", q, x, rows, n)
+    _y64, mag = oracle.matvec_rows_f64("q4k", q, x, rows, n)
+    assert (np.abs(out1 - y_ref) / mag).max() <= 1e-5
+    x2 = (2.0 * x).astype(np.float32)
+    xbuf[:] = x2.tobytes()                      # same buffer object, new contents
+    out2 = f32(b.run()[2])
+    assert np.array_equal(out2, 2.0 * out1)     # scaling x by two is exact in every step of the kernel
+    assert b.run() is b.outputs
+    h.drop()
