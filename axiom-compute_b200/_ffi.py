@@ -121,6 +121,10 @@ SYMBOLS = {
     "axc_cuda_q4k_prefill": (C.c_int, [_VP, _VP, _VP, C.c_uint32, C.c_uint32, C.c_uint32, _VP, _VP]),
     "axc_cuda_q4k_matvec_fused": (C.c_int, [_VP, C.POINTER(AxcXSrc), _VP, C.c_uint32, C.c_uint32,
                                             C.POINTER(AxcGather), _VP, _VP, C.POINTER(AxcTuning)]),
+    "axc_cuda_q4k_prepared_x_bytes": (C.c_size_t, [C.c_uint32]),
+    "axc_cuda_q4k_prepare_x": (C.c_int, [C.POINTER(AxcXSrc), _VP, _VP, C.c_uint32, _VP, _VP, C.c_uint32]),
+    "axc_cuda_q4k_matvec_prepared": (C.c_int, [_VP, _VP, C.c_uint32, _VP, C.c_uint32, C.c_uint32,
+                                               C.POINTER(AxcGather), _VP, _VP, C.POINTER(AxcTuning)]),
     "axc_cuda_gather_next_epoch": (C.c_int, [_VP, _VP]),
     "axc_cuda_gather_finish": (C.c_int, [_VP, _VP, _VP, C.c_uint32, _VP, _VP, C.c_uint32]),
     "axc_cuda_q4k_matvec_static": (C.c_int, [_VP, _VP, _VP, C.c_uint32, C.c_uint32, _VP]),

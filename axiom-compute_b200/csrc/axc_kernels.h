@@ -37,7 +37,8 @@ struct MatvecTuning {
     int pdl = -1;         // programmatic dependent launch: 0 off, 1 on, 2 on + weights before the wait (-1 = default)
     int resident = 0;     // CTAs per SM the shared-memory budget is cut for (0 = default)
     int dry_run = 0;      // compute the launch geometry only, launch nothing
-    const void* x_prepared = nullptr;  // activations already quantised by launch_q4_quantize_x
+    const void* x_prepared = nullptr;  // activations already quantised by a prepare kernel
+    int x_prepared_rms = 0;            // with x_prepared: scale y by 1 / sqrt(mean(x^2))
     const GatherArgs* gather = nullptr;  // all-gather fused into the epilogue (y is ignored)
     const XSource* xsrc = nullptr;       // fused activation source (Q4_K_M only; x is ignored)
 };
@@ -73,6 +74,10 @@ cudaError_t launch_gather_next_epoch(uint32_t* epoch_ptr, cudaStream_t stream);
 // kernel that fills them; a matvec launched with tuning.x_prepared set reads it instead of x.
 size_t q4_prepared_x_bytes(uint32_t n_pos);
 cudaError_t launch_q4_quantize_x(const float* x, void* out, uint32_t n_pos, cudaStream_t stream);
+// The same from a fused source, one CTA per 64 positions, with the per-group sums of x^2 behind
+// the image (for the unit-RMS scale) and optionally x written out as a plain vector.
+cudaError_t launch_q4_prepare_x(const XSource& src, void* image, float* plain_out, uint32_t n_pos, uint32_t* status,
+                                cudaStream_t stream, bool overlap);
 
 cudaError_t launch_q4_0_matvec(const uint8_t* q, const float* x, float* y, uint32_t rows,
                                uint32_t n_blocks, uint32_t* status, cudaStream_t stream,

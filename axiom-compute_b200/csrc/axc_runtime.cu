@@ -831,6 +831,59 @@ int axc_cuda_q4k_matvec_fused(const void* q, const axc_xsrc* xs, float* y, uint3
     return launch_result(axc::launch_q4k_matvec((const uint8_t*)q, nullptr, y, rows, n_superblocks, status, (cudaStream_t)stream, t, sm_count_of_current_device(), nullptr));
 }
 
+size_t axc_cuda_q4k_prepared_x_bytes(uint32_t n_superblocks) { return axc::q4_prepared_x_bytes(n_superblocks * 4u); }
+
+static int check_xsrc(const axc_xsrc* xs) {
+    if (!xs || (!xs->x == !xs->x_pairs) || (xs->x2 && xs->x2_pairs))
+        return fail(AXC_ERR_INVALID_ARGUMENT, "x source: exactly one of x / x_pairs, at most one of x2 / x2_pairs");
+    if ((xs->x_pairs || xs->x2_pairs) && !xs->epoch)
+        return fail(AXC_ERR_INVALID_ARGUMENT, "x source: (value, epoch) vectors need the epoch counter");
+    if (((uintptr_t)xs->x | (uintptr_t)xs->x2 | (uintptr_t)xs->x_pairs | (uintptr_t)xs->x2_pairs) & 15u)
+        return fail(AXC_ERR_INVALID_ARGUMENT, "x sources must be 16-byte aligned");
+    return AXC_OK;
+}
+
+int axc_cuda_q4k_prepare_x(const axc_xsrc* xs, void* image, float* plain_out, uint32_t n_superblocks,
+                           void* stream, uint32_t* status, uint32_t flags) {
+    clear_error();
+    if (n_superblocks == 0) return AXC_OK;
+    int rc = check_xsrc(xs);
+    if (rc != AXC_OK) return rc;
+    if (!image || ((uintptr_t)image & 15u) || ((uintptr_t)plain_out & 15u))
+        return fail(AXC_ERR_INVALID_ARGUMENT, "image must be non-null; image and plain_out 16-byte aligned");
+    if (n_superblocks > 128) return fail(AXC_ERR_INVALID_ARGUMENT, "a prepared x serves rows of 1..128 superblocks");
+    if ((flags & AXC_FINISH_OVERLAP_PREVIOUS) && (xs->x || xs->x2))
+        return fail(AXC_ERR_INVALID_ARGUMENT, "only (value, epoch) sources may overlap the launch before");
+    axc::XSource src;
+    src.x = xs->x, src.x2 = xs->x2, src.x_pairs = xs->x_pairs, src.x2_pairs = xs->x2_pairs, src.epoch_ptr = xs->epoch;
+    return launch_result(axc::launch_q4_prepare_x(src, image, plain_out, n_superblocks * 4u, status, (cudaStream_t)stream,
+                                                  (flags & AXC_FINISH_OVERLAP_PREVIOUS) != 0));
+}
+
+int axc_cuda_q4k_matvec_prepared(const void* q, const void* image, uint32_t unit_rms, float* y, uint32_t rows,
+                                 uint32_t n_superblocks, const axc_gather* g, void* stream, uint32_t* status,
+                                 const axc_tuning* tuning) {
+    clear_error();
+    if (rows == 0) return AXC_OK;
+    if (!q || !image || (((uintptr_t)q | (uintptr_t)image) & 15u))
+        return fail(AXC_ERR_INVALID_ARGUMENT, "q and the prepared x must be non-null and 16-byte aligned");
+    if (n_superblocks == 0 || n_superblocks > 128)
+        return fail(AXC_ERR_INVALID_ARGUMENT, "a prepared x serves rows of 1..128 superblocks");
+    if (!g && (!y || ((uintptr_t)y & 15u)))
+        return fail(AXC_ERR_INVALID_ARGUMENT, "y must be non-null and 16-byte aligned when no all-gather is given");
+    axc::GatherArgs ga{};
+    axc::MatvecTuning t = to_tuning(tuning);
+    if (g) {
+        if (!g->y_peer_bases || !g->epoch || g->world == 0 || g->world > 16 || g->rank >= g->world || (g->y_offset_bytes & 7u))
+            return fail(AXC_ERR_INVALID_ARGUMENT, "incomplete all-gather description");
+        ga.y_peer_bases = g->y_peer_bases, ga.y_offset_bytes = g->y_offset_bytes, ga.epoch_ptr = g->epoch;
+        ga.world = g->world, ga.rank = g->rank, ga.row_offset = g->row_offset;
+        t.gather = &ga;
+    }
+    t.x_prepared = image, t.x_prepared_rms = unit_rms ? 1 : 0;
+    return launch_result(axc::launch_q4k_matvec((const uint8_t*)q, nullptr, y, rows, n_superblocks, status, (cudaStream_t)stream, t, sm_count_of_current_device(), nullptr));
+}
+
 int axc_cuda_gather_next_epoch(uint32_t* epoch, void* stream) {
     clear_error();
     if (!epoch) return fail(AXC_ERR_INVALID_ARGUMENT, "null epoch counter");

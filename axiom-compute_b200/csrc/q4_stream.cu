@@ -54,7 +54,8 @@ constexpr int FMT_Q4K = 0, FMT_Q4_0 = 1;
 struct StreamParams {
     const uint8_t* q;
     const float* x;
-    const void* x_prepared;  // digit words + metadata made by q4_quantize_x_kernel (PREPARED kernels)
+    const void* x_prepared;  // digit words + metadata made by the prepare kernels (PREPARED kernels)
+    uint32_t x_prepared_rms; // PREPARED: scale the result by 1 / sqrt(mean(x^2)) from the image's partial sums
     // Fused x source (XFUSE kernels): x = a [+ b], each either a plain fp32 vector or a vector
     // of (value, epoch) words written by the all-gather epilogue of an earlier call; with
     // x_unit_rms the result is the matvec of x / sqrt(mean(x^2)).
@@ -255,12 +256,12 @@ __device__ __forceinline__ float warp_reduce_transposed(const float (&v)[PASSES]
 template <class Load16>
 __device__ __forceinline__ float quantize_x_positions_from(Load16 load16, uint4* xs, float4* xm,
                                                            uint32_t n_pos, uint32_t pos_end, uint32_t pitch,
-                                                           uint32_t tid, uint32_t nthreads) {
+                                                           uint32_t tid, uint32_t nthreads, uint32_t pos_begin = 0) {
     float sumsq = 0.0f;
     {
         constexpr uint32_t FULL = 0xFFFFFFFFu;
         const uint32_t qt = tid & 3u;
-        for (uint32_t pos = tid >> 2; pos < pos_end; pos += nthreads >> 2) {
+        for (uint32_t pos = pos_begin + (tid >> 2); pos < pos_end; pos += nthreads >> 2) {
             const bool valid = pos < n_pos;
             float4 v[4];
             if (valid) {
@@ -437,10 +438,9 @@ __global__ void __launch_bounds__(512, 1) q4_matvec_stream_kernel(const StreamPa
     }
 
     if constexpr (PREPARED) {
-        // The digit words were produced once by q4_quantize_x_kernel: copy them (and the
-        // per-position sums and scales that follow them) as they are.
-        const uint4* src = reinterpret_cast<const uint4*>(p.x_prepared);
-        for (uint32_t i = tid; i < 17u * p.x_pitch; i += blockDim.x) xs[i] = __ldg(src + i);
+        // The digit words were produced once by a prepare kernel; every thread reads its own
+        // position's words straight into registers below (coalesced: consecutive lanes, consecutive
+        // 16-byte words), so there is nothing to stage and nothing to wait for here.
     } else if constexpr (XFUSE) {
         uint32_t x_epoch = 0;
         if (p.x_pairs || p.x2_pairs)
@@ -478,7 +478,7 @@ __global__ void __launch_bounds__(512, 1) q4_matvec_stream_kernel(const StreamPa
         quantize_x_positions(p.x, xs, xm, p.n_pos, p.x_pos_end, p.x_pitch, tid, blockDim.x);
     }
     if (!p.prefetch_first) start_stream();
-    __syncthreads();
+    if constexpr (!PREPARED) __syncthreads();
     TRACE(2);
 
     LaneCtx ctx;
@@ -491,12 +491,14 @@ __global__ void __launch_bounds__(512, 1) q4_matvec_stream_kernel(const StreamPa
         ctx.mask_a = ctx.big ? 0x0F0Fu : 0x3F3Fu;
         ctx.mask_b = ctx.big ? 0x3030u : 0u;
         const uint32_t pos = active ? my_pos : 0u;
+        const uint4* xs_src = PREPARED ? reinterpret_cast<const uint4*>(p.x_prepared) : xs;
+        const float4* xm_src = PREPARED ? reinterpret_cast<const float4*>(xs_src + 16u * p.x_pitch) : xm;
 #pragma unroll
         for (int k = 0; k < 16; ++k) {
-            const uint4 a = xs[k * p.x_pitch + (pos ^ (uint32_t)(k & 7))];
+            const uint4 a = xs_src[k * p.x_pitch + (pos ^ (uint32_t)(k & 7))];
             ctx.dg[k][0] = a.x, ctx.dg[k][1] = a.y, ctx.dg[k][2] = a.z;
         }
-        const float4 meta = xm[pos];
+        const float4 meta = xm_src[pos];
         ctx.sum_a = meta.x, ctx.sum_b = meta.y, ctx.ps_a = meta.z, ctx.ps_b = meta.w;
     }
 
@@ -570,6 +572,15 @@ __global__ void __launch_bounds__(512, 1) q4_matvec_stream_kernel(const StreamPa
     TRACE(19);
     // x / sqrt(mean(x^2)) as input = the plain result times 1 / sqrt(mean(x^2)).
     float out_scale = 1.0f;
+    if constexpr (PREPARED) {
+        if (p.x_prepared_rms) {   // partial sums of x^2, one per 64 positions, behind the image
+            const float* partial = reinterpret_cast<const float*>(reinterpret_cast<const uint4*>(p.x_prepared) +
+                                                                  17u * p.x_pitch);
+            float tot = 0.0f;
+            for (uint32_t i = 0; i < (p.n_pos + 63u) / 64u; ++i) tot += partial[i];
+            out_scale = 1.0f / sqrtf(tot / (float)(p.n_pos * 64u));
+        }
+    }
     if constexpr (XFUSE) {
         if (p.x_unit_rms) {
             float tot = 0.0f;
@@ -581,7 +592,7 @@ __global__ void __launch_bounds__(512, 1) q4_matvec_stream_kernel(const StreamPa
         for (uint32_t r = tid; r < my_rows; r += blockDim.x) {
             float sum = part[r * wpr];
             for (uint32_t wv = 1; wv < wpr; ++wv) sum += part[r * wpr + wv];
-            if constexpr (XFUSE) sum *= out_scale;
+            if constexpr (XFUSE || PREPARED) sum *= out_scale;
             p.y[r0 + r] = sum;
         }
     } else {
@@ -592,7 +603,7 @@ __global__ void __launch_bounds__(512, 1) q4_matvec_stream_kernel(const StreamPa
         for (uint32_t r = tid; r < my_rows; r += blockDim.x) {
             float sum = part[r * wpr];
             for (uint32_t wv = 1; wv < wpr; ++wv) sum += part[r * wpr + wv];
-            if constexpr (XFUSE) sum *= out_scale;
+            if constexpr (XFUSE || PREPARED) sum *= out_scale;
             const uint64_t word = ((uint64_t)epoch << 32) | (uint64_t)__float_as_uint(sum);
             for (uint32_t pr = 0; pr < p.world; ++pr) {
                 uint64_t* dst = reinterpret_cast<uint64_t*>(peer_base[pr]) + (p.row_offset + r0 + r);
@@ -611,7 +622,7 @@ static cudaError_t launch_stream(const uint8_t* q, const float* x, float* y, uin
                                  LaunchInfo* info) {
     StreamParams p{};
     p.q = q, p.x = x, p.y = y, p.status = status, p.rows = rows;
-    p.x_prepared = tune.x_prepared;
+    p.x_prepared = tune.x_prepared, p.x_prepared_rms = tune.x_prepared_rms ? 1u : 0u;
     p.row_bytes = row_bytes, p.n_pos = n_pos;
     p.warps_per_row = (n_pos + 31) / 32;
     // CTA shape: whole rows per pass, about `threads` threads.  `ctas_per_sm` sizes the grid,
@@ -643,8 +654,9 @@ static cudaError_t launch_stream(const uint8_t* q, const float* x, float* y, uin
 
     const size_t smem_cap = (size_t)(227 * 1024) / resident - 1024;  // 1 KB per CTA is reserved
     p.x_pitch = (n_pos + 7) & ~7u;
-    const size_t xs_bytes = (size_t)16 * p.x_pitch * 16;  // digit words
-    const size_t xm_bytes = (size_t)p.x_pitch * 16;       // per-position sums and scale
+    // digit words and per-position sums/scales; a prepared x is read straight into registers
+    const size_t xs_bytes = tune.x_prepared ? 0 : (size_t)16 * p.x_pitch * 16;
+    const size_t xm_bytes = tune.x_prepared ? 0 : (size_t)p.x_pitch * 16;
     const size_t fixed = (((size_t)p.part_entries * 4 + 64 + 15) & ~(size_t)15) + xs_bytes + xm_bytes;
     int passes = 4;
     if (tune.tile_rows > 0) passes = tune.tile_rows / rows_per_pass;
@@ -689,7 +701,8 @@ static cudaError_t launch_stream(const uint8_t* q, const float* x, float* y, uin
     p.tiles_hi = (p.rows_base + 1 + p.tile_rows - 1) / p.tile_rows;
     p.evict_first = tune.evict_first > 0 ? 1u : 0u;
     p.prefetch_first = tune.pdl >= 2 || tune.pdl < 0 ? 1u : 0u;
-    p.independent = tune.pdl == 3 ? 1u : 0u;
+    // a prepared x is the output of the launch directly before: never read it ahead of the wait
+    p.independent = tune.pdl == 3 && !tune.x_prepared ? 1u : 0u;
 
     void (*kern)(StreamParams) = nullptr;
     if (tune.gather) {
@@ -716,6 +729,12 @@ static cudaError_t launch_stream(const uint8_t* q, const float* x, float* y, uin
                     default: kern = q4_matvec_stream_kernel<FMT, 4, false, false, true>; break;
                 }
             }
+        }
+    } else if (tune.gather && tune.x_prepared) {
+        switch (passes) {
+            case 1: kern = q4_matvec_stream_kernel<FMT, 1, true, true, false>; break;
+            case 2: kern = q4_matvec_stream_kernel<FMT, 2, true, true, false>; break;
+            default: kern = q4_matvec_stream_kernel<FMT, 4, true, true, false>; break;
         }
     } else if (tune.gather) {
         switch (passes) {
@@ -805,9 +824,9 @@ cudaError_t launch_gather_next_epoch(uint32_t* epoch_ptr, cudaStream_t stream) {
     return cudaGetLastError();
 }
 
-// Stand-alone quantiser: writes what the matvec kernel otherwise builds in shared memory
-// (uint4 digit words [16][pitch] followed by float4 metadata [pitch]) to global memory, once,
-// for callers that feed the same x to several matrices or keep the scratch themselves.
+// Stand-alone quantisers: they write what the matvec kernel otherwise builds in shared memory
+// (uint4 digit words [16][pitch], float4 metadata [pitch], then 32 floats: the sum of x^2 of
+// each group of 64 positions) to global memory, once per vector, for every CTA of the consumer.
 __global__ void q4_quantize_x_kernel(const float* __restrict__ x, uint4* __restrict__ out, uint32_t n_pos,
                                      uint32_t pitch) {
     asm volatile("griddepcontrol.wait;" ::: "memory");
@@ -815,13 +834,98 @@ __global__ void q4_quantize_x_kernel(const float* __restrict__ x, uint4* __restr
                          threadIdx.x, blockDim.x);
 }
 
-size_t q4_prepared_x_bytes(uint32_t n_pos) { return (size_t)17 * ((n_pos + 7) & ~7u) * 16; }
+// The same from a fused source (x = a [+ b], plain vectors or (value, epoch) words of an
+// all-gather): one CTA per 64 positions.  Optionally also writes x as a plain fp32 vector.
+// `overlap`: do not wait for the launch before (the sources are epoch words it polls for).
+struct PrepareParams {
+    const float* x;
+    const float* x2;
+    const uint64_t* x_pairs;
+    const uint64_t* x2_pairs;
+    const uint32_t* epoch_ptr;
+    uint4* image;
+    float* plain_out;
+    uint32_t* status;
+    uint32_t n_pos, pitch, overlap;
+};
+
+__global__ void __launch_bounds__(256) q4_prepare_x_kernel(const PrepareParams p) {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    if (!p.overlap) asm volatile("griddepcontrol.wait;" ::: "memory");
+    __shared__ float warp_sq[8];
+    const uint32_t tid = threadIdx.x, lane = tid & 31u, warp = tid >> 5;
+    uint32_t epoch = 0;
+    if (p.x_pairs || p.x2_pairs)
+        asm volatile("ld.relaxed.gpu.global.u32 %0, [%1];" : "=r"(epoch) : "l"(p.epoch_ptr) : "memory");
+    bool gave_up = false;
+    const float4* xa = reinterpret_cast<const float4*>(p.x);
+    const float4* xb = reinterpret_cast<const float4*>(p.x2);
+    float4* po = reinterpret_cast<float4*>(p.plain_out);
+    // whole warps stay in the loop together (it shuffles): the end is rounded up to 8 positions,
+    // positions past n_pos are skipped inside
+    const uint32_t pos0 = blockIdx.x * 64u;
+    const uint32_t pos1 = min(pos0 + 64u, p.pitch);
+    float sq = quantize_x_positions_from(
+        [&](uint32_t i, float4* v) {
+            if (p.x_pairs) {
+                load_pairs16(p.x_pairs, i, epoch, gave_up, v);
+            } else {
+#pragma unroll
+                for (int u = 0; u < 4; ++u) v[u] = __ldg(xa + i + u);
+            }
+            if (p.x2_pairs || xb) {
+                float4 w[4];
+                if (p.x2_pairs) {
+                    load_pairs16(p.x2_pairs, i, epoch, gave_up, w);
+                } else {
+#pragma unroll
+                    for (int u = 0; u < 4; ++u) w[u] = __ldg(xb + i + u);
+                }
+#pragma unroll
+                for (int u = 0; u < 4; ++u) v[u].x += w[u].x, v[u].y += w[u].y, v[u].z += w[u].z, v[u].w += w[u].w;
+            }
+            if (po) {
+#pragma unroll
+                for (int u = 0; u < 4; ++u) po[i + u] = v[u];
+            }
+        },
+        p.image, reinterpret_cast<float4*>(p.image + 16u * p.pitch), p.n_pos, pos1, p.pitch, tid, blockDim.x, pos0);
+    if (gave_up && p.status) atomicOr(p.status, ERR_PEER_WAIT_TIMEOUT);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) sq += __shfl_xor_sync(0xFFFFFFFFu, sq, o);
+    if (lane == 0) warp_sq[warp] = sq;
+    __syncthreads();
+    if (tid == 0) {
+        float tot = 0.0f;
+        for (uint32_t w = 0; w < 8u; ++w) tot += warp_sq[w];
+        reinterpret_cast<float*>(p.image + 17u * p.pitch)[blockIdx.x] = tot;
+    }
+}
+
+size_t q4_prepared_x_bytes(uint32_t n_pos) { return (size_t)17 * ((n_pos + 7) & ~7u) * 16 + 128; }
 
 cudaError_t launch_q4_quantize_x(const float* x, void* out, uint32_t n_pos, cudaStream_t stream) {
     if (n_pos == 0) return cudaSuccess;
     const uint32_t pitch = (n_pos + 7) & ~7u;
     q4_quantize_x_kernel<<<1, 512, 0, stream>>>(x, reinterpret_cast<uint4*>(out), n_pos, pitch);
     return cudaGetLastError();
+}
+
+cudaError_t launch_q4_prepare_x(const XSource& src, void* image, float* plain_out, uint32_t n_pos, uint32_t* status,
+                                cudaStream_t stream, bool overlap) {
+    if (n_pos == 0) return cudaSuccess;
+    if (n_pos > 2048) return cudaErrorInvalidValue;   // 32 partial sums of 64 positions each
+    PrepareParams p{};
+    p.x = src.x, p.x2 = src.x2, p.x_pairs = src.x_pairs, p.x2_pairs = src.x2_pairs, p.epoch_ptr = src.epoch_ptr;
+    p.image = reinterpret_cast<uint4*>(image), p.plain_out = plain_out, p.status = status;
+    p.n_pos = n_pos, p.pitch = (n_pos + 7) & ~7u, p.overlap = overlap ? 1u : 0u;
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3((n_pos + 63) / 64), cfg.blockDim = dim3(256), cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr, cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, q4_prepare_x_kernel, p);
 }
 
 cudaError_t launch_q4k_matvec_segmented(const uint8_t* q, const float* x, float* y, uint32_t rows,

@@ -12,11 +12,17 @@ token's pass through ``layers`` blocks of seven linears with the dataflow
 Every elementwise step is folded into the matvec that consumes it (``axc_cuda_q4k_matvec_fused``:
 x = a [+ b], unit RMS as one output scale), Wq/Wk/Wv and Wgate/Wup are stored as one matrix each,
 so a layer is four launches.  With more than one GPU every linear is row-sharded and its
-all-gather is fused into the producing kernel's epilogue.  Between dependent linears a small
-finish kernel (started while the producer is still running) waits for the (value, epoch) words
-and unpacks them once into a plain vector that every CTA of the consumer then reads through L1;
-``consumer_polls=True`` lets every consumer CTA poll the words itself instead (no launch in
-between, but 2 x the bytes per CTA past L1: measured slower).
+all-gather is fused into the producing kernel's epilogue.  How a linear's output becomes the
+next linear's input is the ``mode``:
+
+* ``"prepared"`` (default): a small prepare kernel between the two (started while the producer is
+  still running when the source is (value, epoch) words) assembles x once, quantises it to the
+  digit-word image and leaves the sums of x^2; every CTA of the consumer reads its digit words
+  straight into registers.
+* ``"fused"``: every consumer CTA assembles and quantises x itself (``axc_cuda_q4k_matvec_fused``);
+  with more than one GPU a finish kernel first unpacks the words into a plain vector.
+* ``"poll"``: as "fused", but every consumer CTA polls the (value, epoch) words itself (no launch in
+  between, 2 x the bytes per CTA past L1: measured slower).
 
 Weights are synthetic (uniform nibbles and scale bytes, d and dmin = f16(|N(0,1)| * 0.01)),
 generated on the device in eight row chunks per linear so that the global matrices are the same
@@ -80,9 +86,12 @@ class DecodeSweep:
     """One rank's share of the stack plus the buffers and launches of a token."""
 
     def __init__(self, shape: SweepShape, device, seed: int = 0xA0C0 + 4 * 16, group=None, tuning=None,
-                 consumer_polls: bool = False):
+                 mode: str = "prepared"):
+        if mode not in ("prepared", "fused", "poll"):
+            raise ValueError("mode must be 'prepared', 'fused' or 'poll'")
         self.shape, self.device = shape, torch.device(device)
-        self.consumer_polls = bool(consumer_polls)
+        self.mode = mode
+        self.consumer_polls = mode == "poll"
         self.world, self.rank = 1, 0
         self.tuning = tuning
         dist_on = group is not None or (torch.distributed.is_available() and torch.distributed.is_initialized()
@@ -133,7 +142,15 @@ class DecodeSweep:
         else:
             self.pairs = None
         self.vec = torch.zeros(words, dtype=torch.float32, device=self.device)
-        if self.world == 1:
+        if self.world == 1 and self.consumer_polls:
+            raise ValueError("mode 'poll' needs more than one rank")
+        k_max = max(k for _n, _r, k in shape.linears)
+        img_bytes = int(_ffi.lib().axc_cuda_q4k_prepared_x_bytes(k_max // 256))
+        self.images = [torch.zeros(img_bytes, dtype=torch.uint8, device=self.device) for _ in range(2)]
+        self._img = 0
+        if self.mode == "prepared":
+            self.launches_per_token = 8 * shape.layers + (3 if self.world > 1 else 1)
+        elif self.world == 1:
             self.launches_per_token = 4 * shape.layers + 1
         elif self.consumer_polls:
             self.launches_per_token = 4 * shape.layers + 3
@@ -156,7 +173,7 @@ class DecodeSweep:
                                self.rank * rows_local)
             rc = _ffi.lib().axc_cuda_q4k_matvec_fused(w.data_ptr(), C.byref(xsrc), None, rows_local, k // 256,
                                                       C.byref(g), self._stream(), st, tn)
-            if rc == 0 and not self.consumer_polls:
+            if rc == 0 and self.mode == "fused":
                 rc = _ffi.lib().axc_cuda_gather_finish(
                     self.pairs.data_ptr() + off * 8, self.epoch.data_ptr(), self.vec.data_ptr() + off * 4, rows,
                     self._stream(), st, _ffi.AXC_FINISH_OVERLAP_PREVIOUS)
@@ -165,10 +182,34 @@ class DecodeSweep:
                                                       rows_local, k // 256, None, self._stream(), st, tn)
         _raise_for(rc)
 
+    def _linear_prepared(self, layer: int, j: int, xsrc: "_ffi.AxcXSrc", rms: bool, overlap: bool) -> None:
+        """prepare_x of the source into the next image buffer, then the matvec that reads it."""
+        _n, rows, k = self.shape.linears[j]
+        rows_local = rows // self.world
+        w = self.weights[layer][j]
+        off = self.offsets[layer][j]
+        st = self.status.data_ptr()
+        tn = C.byref(self.tuning) if self.tuning is not None else None
+        self._img ^= 1
+        img = self.images[self._img].data_ptr()
+        L = _ffi.lib()
+        _raise_for(L.axc_cuda_q4k_prepare_x(C.byref(xsrc), img, None, k // 256, self._stream(), st,
+                                            _ffi.AXC_FINISH_OVERLAP_PREVIOUS if overlap else 0))
+        if self.world > 1:
+            g = _ffi.AxcGather(self.ptr_table.data_ptr(), off * 8, self.epoch.data_ptr(), self.world, self.rank,
+                               self.rank * rows_local)
+            rc = L.axc_cuda_q4k_matvec_prepared(w.data_ptr(), img, 1 if rms else 0, None, rows_local, k // 256,
+                                                C.byref(g), self._stream(), st, tn)
+        else:
+            rc = L.axc_cuda_q4k_matvec_prepared(w.data_ptr(), img, 1 if rms else 0,
+                                                self.vec.data_ptr() + off * 4, rows_local, k // 256, None,
+                                                self._stream(), st, tn)
+        _raise_for(rc)
+
     def _src(self, layer: int, j: int, word: int = 0, second: Optional[int] = None, rms: bool = True):
         """x source = output of linear j of `layer` starting at `word` (+ the vector at `second`)."""
         base = self.offsets[layer][j] + word
-        if self.world > 1 and self.consumer_polls:
+        if self.world > 1 and self.mode != "fused":
             p = self.pairs.data_ptr()
             return _ffi.AxcXSrc(None, None, p + base * 8,
                                 None if second is None else p + (self.offsets[layer][j] + second) * 8,
@@ -186,17 +227,25 @@ class DecodeSweep:
         with torch.cuda.device(self.device):
             if self.world > 1:
                 _raise_for(_ffi.lib().axc_cuda_gather_next_epoch(self.epoch.data_ptr(), self._stream()))
+            prepared = self.mode == "prepared"
+            ov = self.world > 1      # epoch-word sources: the prepare kernel may start behind its producer
             for layer in range(sh.layers):
                 if layer == 0:
                     x = _ffi.AxcXSrc(self.h.data_ptr(), None, None, None, None, 1 if normalise_input else 0)
                 else:
                     x = self._src(layer - 1, 3)                         # h = unitRMS(d of the layer before)
+                if prepared:
+                    self._linear_prepared(layer, 0, x, normalise_input or layer > 0, ov and layer > 0)
+                    self._linear_prepared(layer, 1, self._src(layer, 0), True, ov)
+                    self._linear_prepared(layer, 2, self._src(layer, 1), True, ov)
+                    self._linear_prepared(layer, 3, self._src(layer, 2, 0, sh.ffn), True, ov)
+                    continue
                 self._linear(layer, 0, x)                               # q, k, v
                 self._linear(layer, 1, self._src(layer, 0))             # o = Wo . unitRMS(q): first `hidden` words
                 self._linear(layer, 2, self._src(layer, 1))             # g, u
                 self._linear(layer, 3, self._src(layer, 2, 0, sh.ffn))  # d = Wdown . unitRMS(g + u)
             last = self.offsets[sh.layers - 1][3]
-            if self.world > 1 and self.consumer_polls:
+            if self.world > 1 and self.mode != "fused":
                 # nothing unpacked the words yet: every vector (k and v included) in one pass
                 _raise_for(_ffi.lib().axc_cuda_gather_finish(
                     self.pairs.data_ptr(), self.epoch.data_ptr(), self.vec.data_ptr(),

@@ -281,6 +281,7 @@ int axc_cuda_q4k_prefill(const void* q, const uint16_t* a_bf16, float* c, uint32
  * (fp32).  y receives the rows when g is NULL; with g the rows go into every rank's vector as
  * for axc_cuda_q4k_matvec_allgather.  No counterpart in the reference (it has neither a
  * multi-GPU path nor a model); this is the linear layer of the 70B-shaped decode sweep. */
+#define AXC_FINISH_OVERLAP_PREVIOUS 1u
 typedef struct axc_xsrc {
     const float* x;
     const float* x2;
@@ -292,13 +293,28 @@ typedef struct axc_xsrc {
 int axc_cuda_q4k_matvec_fused(const void* q, const axc_xsrc* xs, float* y, uint32_t rows,
                               uint32_t n_superblocks, const axc_gather* g, void* stream,
                               uint32_t* status, const axc_tuning* tuning);
+/* The same work split in two launches, for vectors that many CTAs consume: prepare_x assembles
+ * x = a [+ b] once (one CTA per 64 x 64 columns), quantises it to the digit-word image the matvec
+ * kernels otherwise build per CTA in shared memory, stores the per-group sums of x^2 behind it and
+ * optionally writes x out as a plain fp32 vector (plain_out may be NULL); matvec_prepared then
+ * reads its digit words straight into registers (no staging, no CTA-wide barrier) and, with
+ * unit_rms != 0, scales by 1 / sqrt(mean(x^2)).  image: axc_cuda_q4k_prepared_x_bytes(n) bytes of
+ * 16-byte aligned device memory.  flags: AXC_FINISH_OVERLAP_PREVIOUS (epoch-word sources only)
+ * lets prepare_x start before the launch directly before it has completed.  matvec_prepared
+ * must directly follow the prepare_x of its image in the same stream, or a launch that does not
+ * write the image.  No counterpart in the reference. */
+size_t axc_cuda_q4k_prepared_x_bytes(uint32_t n_superblocks);
+int axc_cuda_q4k_prepare_x(const axc_xsrc* xs, void* image, float* plain_out, uint32_t n_superblocks,
+                           void* stream, uint32_t* status, uint32_t flags);
+int axc_cuda_q4k_matvec_prepared(const void* q, const void* image, uint32_t unit_rms, float* y, uint32_t rows,
+                                 uint32_t n_superblocks, const axc_gather* g, void* stream, uint32_t* status,
+                                 const axc_tuning* tuning);
 /* *epoch += 1, in stream order (a one-thread kernel). */
 int axc_cuda_gather_next_epoch(uint32_t* epoch, void* stream);
 /* Consumer side: pairs = this rank's own pair storage (n words), out = n fp32 values.
  * flags: AXC_FINISH_OVERLAP_PREVIOUS lets the kernel start before the launch directly before it
  * in the stream has completed (it polls for that launch's words anyway); the caller guarantees
  * that launch neither advances the epoch nor reads or writes `out`. */
-#define AXC_FINISH_OVERLAP_PREVIOUS 1u
 int axc_cuda_gather_finish(const uint64_t* pairs, const uint32_t* epoch, float* out, uint32_t n,
                            void* stream, uint32_t* status, uint32_t flags);
 

@@ -119,11 +119,57 @@ def test_gather_finish_overlapping_its_producer(ffi, ops, synth):
     assert int(st.item()) == 0
 
 
-def test_decode_sweep_matches_oracle_on_a_small_stack():
+@pytest.mark.parametrize("rows,n_sb", [(33, 1), (257, 16), (64, 112), (300, 128)])
+@pytest.mark.parametrize("second,rms", [(False, False), (True, True)])
+def test_prepared_x_matches_oracle(ffi, ops, synth, rows, n_sb, second, rms):
+    """prepare_x + matvec_prepared: same results as the oracle on x = a [+ b] (unit RMS optional);
+    the plain copy of x that prepare_x can emit is exact."""
+    q = synth.q4k_weights(rows, n_sb, 7700 + rows + n_sb)
+    a = synth.activations(n_sb * 256, 7710 + rows)
+    b = synth.activations(n_sb * 256, 7720 + rows)
+    x = (a + b).astype(np.float32) if second else a
+    x_eff = oracle.unit_rms(x) if rms else x
+    y_ref = oracle.matvec_rows("q4k", q, x_eff, rows, n_sb)
+    _y64, mag = oracle.matvec_rows_f64("q4k", q, x_eff, rows, n_sb)
+    L = ffi.lib()
+    img = torch.zeros(int(L.axc_cuda_q4k_prepared_x_bytes(n_sb)), dtype=torch.uint8, device="cuda")
+    plain = torch.zeros(n_sb * 256, device="cuda")
+    y = torch.empty(rows, device="cuda")
+    st = ops.new_status()
+    ad, bd, qd = dev(a), dev(b), dev(q)
+    xs = ffi.AxcXSrc(ad.data_ptr(), bd.data_ptr() if second else None, None, None, None, 0)
+    s = int(torch.cuda.current_stream().cuda_stream)
+    for _ in range(2):
+        assert L.axc_cuda_q4k_prepare_x(C.byref(xs), img.data_ptr(), plain.data_ptr(), n_sb, s, st.data_ptr(), 0) == 0
+        assert L.axc_cuda_q4k_matvec_prepared(qd.data_ptr(), img.data_ptr(), 1 if rms else 0, y.data_ptr(), rows, n_sb,
+                                              None, s, st.data_ptr(), None) == 0
+    torch.cuda.synchronize()
+    assert int(st.item()) == 0
+    assert np.array_equal(plain.cpu().numpy(), x)
+    assert (np.abs(y.cpu().numpy() - y_ref) / mag).max() <= NORMWISE_TOL
+
+
+def test_prepare_x_argument_checks(ffi, synth):
+    L = ffi.lib()
+    x = dev(synth.activations(256, 7801))
+    pairs = torch.zeros(256, dtype=torch.int64, device="cuda")
+    img = torch.zeros(int(L.axc_cuda_q4k_prepared_x_bytes(1)), dtype=torch.uint8, device="cuda")
+    s = int(torch.cuda.current_stream().cuda_stream)
+    plain_src = ffi.AxcXSrc(x.data_ptr(), None, None, None, None, 0)
+    assert L.axc_cuda_q4k_prepare_x(C.byref(plain_src), None, None, 1, s, None, 0) == 100
+    assert L.axc_cuda_q4k_prepare_x(C.byref(plain_src), img.data_ptr(), None, 129, s, None, 0) == 100
+    assert L.axc_cuda_q4k_prepare_x(C.byref(plain_src), img.data_ptr(), None, 1, s, None, 1) == 100   # plain source may not overlap
+    no_epoch = ffi.AxcXSrc(None, None, pairs.data_ptr(), None, None, 0)
+    assert L.axc_cuda_q4k_prepare_x(C.byref(no_epoch), img.data_ptr(), None, 1, s, None, 0) == 100
+    assert L.axc_cuda_q4k_prepared_x_bytes(16) == 17 * 64 * 16 + 128
+
+
+@pytest.mark.parametrize("mode", ["prepared", "fused"])
+def test_decode_sweep_matches_oracle_on_a_small_stack(mode):
     decode = load_pkg("decode")
     shape = decode.SweepShape(hidden=512, kv=128, ffn=1024, layers=3)
-    sweep = decode.DecodeSweep(shape, "cuda", seed=4242)
-    assert sweep.world == 1 and sweep.launches_per_token == 13
+    sweep = decode.DecodeSweep(shape, "cuda", seed=4242, mode=mode)
+    assert sweep.world == 1 and sweep.launches_per_token == (25 if mode == "prepared" else 13)
     rng = np.random.default_rng(5)
     h0 = rng.standard_normal(shape.hidden).astype(np.float32)
     weights = [tuple(w.cpu().numpy() for w in layer) for layer in sweep.weights]
