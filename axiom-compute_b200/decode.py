@@ -15,11 +15,11 @@ so a layer is four launches.  With more than one GPU every linear is row-sharded
 all-gather is fused into the producing kernel's epilogue.  How a linear's output becomes the
 next linear's input is the ``mode``:
 
-* ``"prepared"`` (default): a small prepare kernel between the two (started while the producer is
+* ``"prepared"`` (default on one GPU): a small prepare kernel between the two (started while the producer is
   still running when the source is (value, epoch) words) assembles x once, quantises it to the
   digit-word image and leaves the sums of x^2; every CTA of the consumer reads its digit words
   straight into registers.
-* ``"fused"``: every consumer CTA assembles and quantises x itself (``axc_cuda_q4k_matvec_fused``);
+* ``"fused"`` (default on several GPUs): every consumer CTA assembles and quantises x itself (``axc_cuda_q4k_matvec_fused``);
   with more than one GPU a finish kernel first unpacks the words into a plain vector.
 * ``"poll"``: as "fused", but every consumer CTA polls the (value, epoch) words itself (no launch in
   between, 2 x the bytes per CTA past L1: measured slower).
@@ -86,7 +86,11 @@ class DecodeSweep:
     """One rank's share of the stack plus the buffers and launches of a token."""
 
     def __init__(self, shape: SweepShape, device, seed: int = 0xA0C0 + 4 * 16, group=None, tuning=None,
-                 mode: str = "prepared"):
+                 mode: str = "auto"):
+        if mode == "auto":   # the faster one as measured: prepared on one GPU, fused + finish on several
+            multi = torch.distributed.is_available() and torch.distributed.is_initialized() \
+                and torch.distributed.get_world_size(group) > 1
+            mode = "fused" if multi else "prepared"
         if mode not in ("prepared", "fused", "poll"):
             raise ValueError("mode must be 'prepared', 'fused' or 'poll'")
         self.shape, self.device = shape, torch.device(device)

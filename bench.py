@@ -560,7 +560,7 @@ def run_decode(args):
         "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
         "config": {"workload": f"70B-shaped decode sweep, {shape.layers} layers x (qkv 10240x8192, o 8192x8192, "
                                "gate+up 57344x8192, down 8192x28672) Q4_K_M, batch 1",
-                   "weight_bytes": weight_bytes, "exchange": args.decode_mode, "launch": "cuda_graph" if graph is not None else "stream",
+                   "weight_bytes": weight_bytes, "exchange": sweep.mode, "launch": "cuda_graph" if graph is not None else "stream",
                    "l2": "inputs larger than L2: every token streams all weights once",
                    "parallelism": "single GPU" if world == 1 else
                                   f"rows of every linear sharded over {world} GPUs, all-gather fused into the "
@@ -660,7 +660,7 @@ def main():
     ap.add_argument("--workload", choices=["matvec", "decode70b", "prefill"], default="matvec",
                     help="matvec: the headline 14336 x 4096 metric; decode70b: the 70B-shaped decode sweep")
     ap.add_argument("--layers", type=int, default=80, help="decode70b: layers in the stack")
-    ap.add_argument("--decode-mode", choices=["prepared", "fused", "poll"], default="prepared",
+    ap.add_argument("--decode-mode", choices=["auto", "prepared", "fused", "poll"], default="auto",
                     help="decode70b: how a linear's output reaches the next linear (see decode.py)")
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=2000)

@@ -168,6 +168,7 @@ def test_prepare_x_argument_checks(ffi, synth):
 def test_decode_sweep_matches_oracle_on_a_small_stack(mode):
     decode = load_pkg("decode")
     shape = decode.SweepShape(hidden=512, kv=128, ffn=1024, layers=3)
+    assert decode.DecodeSweep(decode.SweepShape(256, 64, 256, 1), "cuda").mode == "prepared"   # auto, one GPU
     sweep = decode.DecodeSweep(shape, "cuda", seed=4242, mode=mode)
     assert sweep.world == 1 and sweep.launches_per_token == (25 if mode == "prepared" else 13)
     rng = np.random.default_rng(5)
