@@ -63,7 +63,14 @@ struct Slot {
     void* staging = nullptr;  // pinned
     uint64_t size = 0;        // allocated bytes (power of two)
     uint64_t valid = 0;       // bytes of the most recent upload
+    bool mapped = false;      // dev is the device view of the pinned host buffer (no copies)
 };
+
+// Output bindings up to this size live in mapped pinned host memory: the kernel's stores go
+// straight to the host over PCIe and the device-to-host copy (a second DMA after the kernel,
+// several microseconds of latency for a few tens of KB) disappears.  Larger outputs keep a
+// device buffer and one bulk copy.
+constexpr uint64_t kMappedOutputMax = 1u << 20;
 
 struct CacheKey {
     uint64_t spirv_hash, plan_hash;
@@ -123,7 +130,7 @@ struct DeviceGuard {
 };
 
 void free_slot(Slot& s) {
-    if (s.dev) cudaFree(s.dev);
+    if (s.dev && !s.mapped) cudaFree(s.dev);
     if (s.staging) cudaFreeHost(s.staging);
     s = Slot{};
 }
@@ -131,8 +138,7 @@ void free_slot(Slot& s) {
 void destroy_kernel(axc_kernel* k) {
     DeviceGuard g(k->device);
     for (auto& s : k->slots) free_slot(s);
-    if (k->status_dev) cudaFree(k->status_dev);
-    if (k->status_host) cudaFreeHost(k->status_host);
+    if (k->status_host) cudaFreeHost(k->status_host);   // status_dev is its device view
     for (auto& e : k->ev)
         if (e) cudaEventDestroy(e);
     delete k;
@@ -172,7 +178,7 @@ bool wait_event(cudaEvent_t ev, uint64_t timeout_ms, cudaError_t* err) {
     }
 }
 
-int ensure_slots(axc_kernel* k, const size_t* input_lens, const size_t* output_sizes) {
+int ensure_slots(axc_kernel* k, const size_t* input_lens, const size_t* output_sizes, const bool* writable) {
     if (k->slots.size() < k->n_bufs) k->slots.resize(k->n_bufs);
     for (uint32_t i = 0; i < k->n_bufs; ++i) {
         const uint64_t need = std::max<uint64_t>(std::max<uint64_t>(input_lens[i], output_sizes[i]), 4);
@@ -184,6 +190,18 @@ int ensure_slots(axc_kernel* k, const size_t* input_lens, const size_t* output_s
         if (new_size == UINT64_MAX)
             return fail(AXC_ERR_BUFFER_ALLOCATION_FAILED, "buffer #%u allocation failed (%llu bytes): requested size too large (> 2^62 bytes)", i, (unsigned long long)need);
         free_slot(s);
+        if (writable && writable[i] && new_size <= kMappedOutputMax) {
+            cudaError_t em = cudaHostAlloc(&s.staging, new_size, cudaHostAllocMapped);
+            if (em == cudaSuccess) em = cudaHostGetDevicePointer(&s.dev, s.staging, 0);
+            if (em == cudaSuccess) {
+                std::memset(s.staging, 0, new_size);
+                s.size = new_size, s.valid = 0, s.mapped = true;
+                continue;
+            }
+            if (s.staging) cudaFreeHost(s.staging);
+            s = Slot{};
+            cudaGetLastError();   // fall back to a device buffer + staging copy
+        }
         cudaError_t e = cudaMalloc(&s.dev, new_size);
         if (e != cudaSuccess) {
             s = Slot{};
@@ -252,7 +270,8 @@ int dispatch_locked(axc_ctx* ctx, axc_kernel* k, const uint32_t wg[3], const voi
                     const size_t* input_lens, void* const* outputs, const size_t* output_sizes,
                     const void* pc, axc_dispatch_stats* stats) {
     DeviceGuard g(k->device);
-    int rc = ensure_slots(k, input_lens, output_sizes);
+    const bool writable[3] = {false, false, true};   // both kernels: [q, x] read-only, y written
+    int rc = ensure_slots(k, input_lens, output_sizes, k->n_bufs == 3 ? writable : nullptr);
     if (rc != AXC_OK) return rc;
     cudaStream_t st = ctx->stream;
     const bool timed = stats != nullptr;
@@ -263,6 +282,8 @@ int dispatch_locked(axc_ctx* ctx, axc_kernel* k, const uint32_t wg[3], const voi
         if (input_lens[i] == 0) continue;  // resident: keep device contents
         Slot& s = k->slots[i];
         std::memcpy(s.staging, inputs[i], input_lens[i]);
+        s.valid = input_lens[i];
+        if (s.mapped) continue;   // the device reads the pinned buffer itself
         e = cudaMemcpyAsync(s.dev, s.staging, input_lens[i], cudaMemcpyHostToDevice, st);
         if (e != cudaSuccess) {
             g_fields.binding = i, g_fields.direction = AXC_COPY_HOST_TO_DEVICE;
@@ -321,14 +342,14 @@ int dispatch_locked(axc_ctx* ctx, axc_kernel* k, const uint32_t wg[3], const voi
     for (uint32_t i = 0; i < k->n_bufs; ++i) {
         if (output_sizes[i] == 0) continue;
         Slot& s = k->slots[i];
+        if (s.mapped) continue;   // already in host memory when the event completes
         e = cudaMemcpyAsync(s.staging, s.dev, output_sizes[i], cudaMemcpyDeviceToHost, st);
         if (e != cudaSuccess) {
             g_fields.binding = i, g_fields.direction = AXC_COPY_DEVICE_TO_HOST;
             return fail(AXC_ERR_STAGING_COPY_FAILED, "staging copy failed for binding #%u (DeviceToHost): %s", i, cudaGetErrorString(e));
         }
     }
-    e = cudaMemcpyAsync(k->status_host, k->status_dev, 4, cudaMemcpyDeviceToHost, st);
-    if (e == cudaSuccess) e = cudaEventRecord(timed ? k->ev[3] : k->ev[4], st);
+    e = cudaEventRecord(timed ? k->ev[3] : k->ev[4], st);
     if (e != cudaSuccess)
         return fail(AXC_ERR_QUEUE_SUBMIT_FAILED, "queue submit failed: %s", cudaGetErrorString(e));
 
@@ -343,7 +364,7 @@ int dispatch_locked(axc_ctx* ctx, axc_kernel* k, const uint32_t wg[3], const voi
     }
     if (*k->status_host != 0) {
         const uint32_t bits = *k->status_host;
-        cudaMemsetAsync(k->status_dev, 0, 4, st);
+        *k->status_host = 0;
         g_fields.timeout_ns = 0;
         return fail(AXC_ERR_FENCE_TIMEOUT, "fence wait timed out after 0 ns: kernel gave up waiting for its weight stream (status bits 0x%x)", bits);
     }
@@ -549,9 +570,13 @@ int axc_cuda_prepare_kernel(axc_ctx* ctx, const char* entry_point, const axc_buf
     k->n_bufs = n_bufs;
     k->pc_total = pc_total_bytes;
     DeviceGuard g(ctx->device);
-    cudaError_t e = cudaMalloc((void**)&k->status_dev, 4);
-    if (e == cudaSuccess) e = cudaMemset(k->status_dev, 0, 4);
-    if (e == cudaSuccess) e = cudaHostAlloc((void**)&k->status_host, 4, cudaHostAllocDefault);
+    // The kernel's error word lives in mapped pinned host memory: it is written only when a
+    // bounded wait gives up, and reading it back costs no copy after the kernel.
+    cudaError_t e = cudaHostAlloc((void**)&k->status_host, 64, cudaHostAllocMapped);
+    if (e == cudaSuccess) {
+        *k->status_host = 0;
+        e = cudaHostGetDevicePointer((void**)&k->status_dev, k->status_host, 0);
+    }
     for (auto& ev : k->ev)
         if (e == cudaSuccess) e = cudaEventCreate(&ev);
     if (e != cudaSuccess) {

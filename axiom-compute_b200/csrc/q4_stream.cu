@@ -34,18 +34,13 @@
 // from the dequant kernels, which share the unpack code).  Row sums: transposed warp-shuffle
 // reduction, per-warp partials in shared memory, one fixed-order combine per CTA at the end
 // (deterministic).
+#include <map>
+#include <mutex>
+#include <utility>
+
 #include "axc_device.cuh"
 #include "axc_kernels.h"
 
-#ifdef AXC_TRACE
-__device__ unsigned long long g_axc_trace[2048 * 24];
-#define TRACE(slot) do { if (tid == 0) { unsigned long long t_; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_)); g_axc_trace[blockIdx.x * 24 + (slot)] = t_; } } while (0)
-extern "C" int axc_debug_copy_trace(unsigned long long* dst, int n) {
-    return (int)cudaMemcpyFromSymbol(dst, g_axc_trace, sizeof(unsigned long long) * n);
-}
-#else
-#define TRACE(slot) do { } while (0)
-#endif
 
 namespace axc {
 
@@ -364,7 +359,6 @@ __global__ void __launch_bounds__(512, 1) q4_matvec_stream_kernel(const StreamPa
 
     // Let the next grid in the stream be scheduled as early as the hardware allows.
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-    TRACE(0);
 
     // Rows owned by this CTA: an even split computed on the host (no CTA has more than one
     // extra row).
@@ -426,7 +420,6 @@ __global__ void __launch_bounds__(512, 1) q4_matvec_stream_kernel(const StreamPa
     // A caller that knows neither is the case (say the up projection launched right after the
     // gate projection of the same x) lets the whole prologue overlap the previous kernel.
     if (!p.independent) asm volatile("griddepcontrol.wait;" ::: "memory");
-    TRACE(1);
     // Fused all-gather: the peer addresses never change; the epoch was advanced by an earlier
     // kernel of the stream, so it is read on this side of the wait (through L2, not a cached line).
     __shared__ uint64_t peer_base[16];
@@ -479,7 +472,6 @@ __global__ void __launch_bounds__(512, 1) q4_matvec_stream_kernel(const StreamPa
     }
     if (!p.prefetch_first) start_stream();
     if constexpr (!PREPARED) __syncthreads();
-    TRACE(2);
 
     LaneCtx ctx;
     {
@@ -502,7 +494,6 @@ __global__ void __launch_bounds__(512, 1) q4_matvec_stream_kernel(const StreamPa
         ctx.sum_a = meta.x, ctx.sum_b = meta.y, ctx.ps_a = meta.z, ctx.ps_b = meta.w;
     }
 
-    TRACE(3);
     // Lanes past the end of the row read position 0 and are zeroed below.
     const uint32_t pos_off = !active ? 0u : FMT == FMT_Q4K ? (my_pos >> 2) * Q4K_SB_BYTES : my_pos * 36u;
     const uint8_t* lane_base = ring + pos_off + row_in_pass * row_bytes;
@@ -522,7 +513,6 @@ __global__ void __launch_bounds__(512, 1) q4_matvec_stream_kernel(const StreamPa
     uint32_t s = 0, parity = 0, rows_left = my_rows;
     for (uint32_t tile = 0; tile < n_tiles; ++tile) {
         if (!mbar_wait(&full[s], parity, p.status)) break;  // status word set; y stays partial
-        if (tile < 14) TRACE(4 + tile);
         const uint8_t* sp = lane_base + s * p.stage_bytes + delta;
 
         float v[PASSES];
@@ -562,14 +552,12 @@ __global__ void __launch_bounds__(512, 1) q4_matvec_stream_kernel(const StreamPa
         if (++s == p.stages) s = 0, parity ^= 1u;
     }
 
-    TRACE(18);
     __syncthreads();
     if (p.independent) {
         asm volatile("griddepcontrol.wait;" ::: "memory");  // stream order for y
         if constexpr (GATHER)
             asm volatile("ld.relaxed.gpu.global.u32 %0, [%1];" : "=r"(epoch) : "l"(p.epoch_ptr) : "memory");
     }
-    TRACE(19);
     // x / sqrt(mean(x^2)) as input = the plain result times 1 / sqrt(mean(x^2)).
     float out_scale = 1.0f;
     if constexpr (PREPARED) {
@@ -614,6 +602,22 @@ __global__ void __launch_bounds__(512, 1) q4_matvec_stream_kernel(const StreamPa
 }
 
 // ---------------------------------------------------------------------------------------------
+
+// cudaFuncSetAttribute costs a microsecond or two of host time: raise a kernel's dynamic
+// shared-memory limit only when a launch needs more than an earlier one set (per device).
+static cudaError_t ensure_dynamic_smem(const void* kern, size_t smem) {
+    static std::mutex mu;
+    static std::map<std::pair<int, const void*>, size_t> limit;
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return e;
+    std::lock_guard<std::mutex> lock(mu);
+    size_t& have = limit[{dev, kern}];
+    if (smem <= have) return cudaSuccess;
+    e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e == cudaSuccess) have = smem;
+    return e;
+}
 
 template <int FMT>
 static cudaError_t launch_stream(const uint8_t* q, const float* x, float* y, uint32_t rows,
@@ -761,7 +765,7 @@ static cudaError_t launch_stream(const uint8_t* q, const float* x, float* y, uin
         info->n_seg = 1;
     }
     if (tune.dry_run) return cudaSuccess;
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    cudaError_t e = ensure_dynamic_smem(reinterpret_cast<const void*>(kern), smem);
     if (e != cudaSuccess) return e;
 
     cudaLaunchConfig_t cfg{};
