@@ -13,6 +13,14 @@
 //            even) into the K-major 128-byte-swizzled operand tile, then run the epilogue
 //            (tcgen05.ld of the accumulators, coalesced stores of C)
 //
+// Two forms.  Single: one CTA per tile, `tcgen05.mma.cta_group::1`.  Pair (default): two CTAs of
+// a cluster work as one 256-row tile with `tcgen05.mma.cta_group::2`: each CTA dequantises its own
+// 128 rows and holds half of every 256-token block, so per SM the token loads and the B-operand
+// reads are halved (with one CTA the shared-memory port, not the tensor pipe, is the limit).  The
+// leader CTA issues the MMAs for both; the peer tells the leader's barriers (remote mbarrier
+// arrives) when its tiles are ready, and `tcgen05.commit` with cluster multicast frees the stages
+// in both CTAs.  TMA loads are CTA-local in both forms (no multicast loads).
+//
 // Every wait on an mbarrier is bounded; a wait that runs out sets an error bit and an abort flag,
 // all roles fall through to the common exit, outstanding copies are waited for and tensor memory
 // is freed.
@@ -29,12 +37,12 @@ namespace {
 constexpr uint32_t PF_ROWS = 128;                 // weight rows per CTA = MMA M
 constexpr uint32_t PF_TOK = 256;                  // tokens per MMA = MMA N
 constexpr uint32_t PF_TOK_MAX = 512;              // tokens per CTA (all of tensor memory)
-constexpr uint32_t PF_A_STAGES = 2, PF_W_STAGES = 3, PF_RAW_STAGES = 2;
-constexpr uint32_t PF_A_HALF_BYTES = PF_TOK * 128;            // 256 tokens x 64 bf16
-constexpr uint32_t PF_A_BYTES = 2 * PF_A_HALF_BYTES;          // 65536
+constexpr uint32_t PF_W_STAGES = 3, PF_RAW_STAGES = 2;
+constexpr uint32_t PF_A_REGION = 131072;                      // token stages: 2 x 64 KB (single) or 4 x 32 KB (pair)
+constexpr uint32_t PF_MAX_A_STAGES = 4;
 constexpr uint32_t PF_W_BYTES = PF_ROWS * 128;                // 128 rows x 64 bf16
 constexpr uint32_t PF_RAW_BYTES = PF_ROWS * Q4K_SB_BYTES;     // 18432
-constexpr uint32_t PF_OFF_W = PF_A_STAGES * PF_A_BYTES;                       // 131072
+constexpr uint32_t PF_OFF_W = PF_A_REGION;                                     // 131072
 constexpr uint32_t PF_OFF_RAW = PF_OFF_W + PF_W_STAGES * PF_W_BYTES;           // 180224
 constexpr uint32_t PF_OFF_BAR = PF_OFF_RAW + PF_RAW_STAGES * PF_RAW_BYTES;     // 217088
 constexpr uint32_t PF_SMEM = PF_OFF_BAR + 256 + 1024;                          // + alignment slack
@@ -44,6 +52,8 @@ constexpr uint32_t PF_THREADS = (3 + PF_DEQ_WARPS) * 32;
 // kind::f16 instruction descriptor: fp32 accumulate, bf16 x bf16, both operands K-major,
 // N = 256 (field N >> 3 at bit 17), M = 128 (field M >> 4 at bit 24).
 constexpr uint32_t PF_IDESC = (1u << 4) | (1u << 7) | (1u << 10) | ((PF_TOK >> 3) << 17) | ((PF_ROWS >> 4) << 24);
+// the pair form: M = 256 over the two CTAs
+constexpr uint32_t PF_IDESC_PAIR = (1u << 4) | (1u << 7) | (1u << 10) | ((PF_TOK >> 3) << 17) | ((256u >> 4) << 24);
 
 // Shared-memory matrix descriptor of a K-major tile whose rows are 128 bytes (64 bf16) with the
 // 128-byte swizzle: start address / 16, leading offset 1 (unused with a swizzle), stride between
@@ -72,6 +82,57 @@ __device__ __forceinline__ void umma_bf16(uint32_t d_tmem, uint64_t a_desc, uint
         : "memory");
 }
 
+__device__ __forceinline__ void umma_bf16_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
+        "l"(a_desc), "l"(b_desc), "r"(PF_IDESC_PAIR), "r"(accumulate)
+        : "memory");
+}
+
+// Arrives (once the MMAs issued so far have completed) on the barrier at this shared-memory
+// offset in both CTAs of the pair.
+__device__ __forceinline__ void umma_commit_pair(uint64_t* bar) {
+    asm volatile(
+        "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::"r"(
+            smem_u32(bar)),
+        "h"((uint16_t)3)
+        : "memory");
+}
+
+// Arrive on the barrier at the same offset in CTA `cta` of the cluster.
+__device__ __forceinline__ void mbar_arrive_remote(uint64_t* bar, uint32_t cta) {
+    asm volatile(
+        "{\n\t.reg .b32 r;\n\t"
+        "mapa.shared::cluster.u32 r, %0, %1;\n\t"
+        "mbarrier.arrive.release.cluster.shared::cluster.b64 _, [r];\n\t}" ::"r"(smem_u32(bar)),
+        "r"(cta)
+        : "memory");
+}
+
+// Bounded wait that also acquires what other CTAs of the cluster released before arriving.
+__device__ __forceinline__ bool mbar_wait_cluster(uint64_t* bar, uint32_t parity, uint32_t* err) {
+    const uint32_t addr = smem_u32(bar);
+    for (uint32_t it = 0; it < MBAR_SPIN_LIMIT; ++it) {
+        uint32_t done;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t}"
+            : "=r"(done)
+            : "r"(addr), "r"(parity)
+            : "memory");
+        if (done) return true;
+    }
+    if (err) atomicOr(err, ERR_BULK_WAIT_TIMEOUT);
+    return false;
+}
+
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+
 __device__ __forceinline__ void umma_commit(uint64_t* bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
                  : "memory");
@@ -84,7 +145,7 @@ __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
 }
 
 struct PfBars {
-    uint64_t a_full[PF_A_STAGES], a_empty[PF_A_STAGES];
+    uint64_t a_full[PF_MAX_A_STAGES], a_empty[PF_MAX_A_STAGES];
     uint64_t w_full[PF_W_STAGES], w_empty[PF_W_STAGES];
     uint64_t raw_full[PF_RAW_STAGES], raw_empty[PF_RAW_STAGES];
     uint64_t acc_full;
@@ -92,6 +153,7 @@ struct PfBars {
     volatile uint32_t abort;
 };
 
+template <bool PAIR>
 __global__ void __launch_bounds__(PF_THREADS, 1)
 q4k_prefill_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_w,
                    float* __restrict__ c, uint32_t m_total, uint32_t n_rows, uint32_t n_sb, uint32_t* status) {
@@ -107,11 +169,21 @@ q4k_prefill_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_consta
     const uint32_t m_count = min(PF_TOK_MAX, m_total - m0);
     const uint32_t halves = (m_count + PF_TOK - 1) / PF_TOK;
     const uint32_t n_kb = n_sb * 4;
+    // Pair form: CTA `rank` of the cluster holds tokens [rank * 128, rank * 128 + 128) of every
+    // 256-token block; rank 0 (the leader) issues the MMAs.
+    constexpr uint32_t A_STAGES = PAIR ? 4u : 2u;
+    constexpr uint32_t A_HALF_BYTES = PAIR ? 128u * 128u : PF_TOK * 128u;   // one block's share per CTA
+    constexpr uint32_t A_BYTES = 2u * A_HALF_BYTES;
+    uint32_t rank = 0;
+    if constexpr (PAIR) asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(rank));
+    const bool leader = rank == 0;
 
     if (tid == 0) {
-        for (uint32_t s = 0; s < PF_A_STAGES; ++s) mbar_init(&bars->a_full[s], 1), mbar_init(&bars->a_empty[s], 1);
+        // pair: the leader's "full" barriers also count the peer (its relay thread / its dequant warps)
+        const uint32_t both = PAIR && leader ? 2u : 1u;
+        for (uint32_t s = 0; s < A_STAGES; ++s) mbar_init(&bars->a_full[s], both), mbar_init(&bars->a_empty[s], 1);
         for (uint32_t s = 0; s < PF_W_STAGES; ++s)
-            mbar_init(&bars->w_full[s], PF_DEQ_WARPS), mbar_init(&bars->w_empty[s], 1);
+            mbar_init(&bars->w_full[s], PF_DEQ_WARPS * both), mbar_init(&bars->w_empty[s], 1);
         for (uint32_t s = 0; s < PF_RAW_STAGES; ++s)
             mbar_init(&bars->raw_full[s], 1), mbar_init(&bars->raw_empty[s], PF_DEQ_WARPS);
         mbar_init(&bars->acc_full, 1);
@@ -119,13 +191,23 @@ q4k_prefill_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_consta
         mbar_init_fence();
     }
     if (warp == 2) {  // tensor memory: all 512 columns (this kernel runs one CTA per SM)
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&bars->tmem_base)),
-                     "r"(512u)
-                     : "memory");
-        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+        if constexpr (PAIR) {
+            asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+                             smem_u32(&bars->tmem_base)),
+                         "r"(512u)
+                         : "memory");
+            asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+        } else {
+            asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+                             smem_u32(&bars->tmem_base)),
+                         "r"(512u)
+                         : "memory");
+            asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+        }
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
+    if constexpr (PAIR) cluster_sync_all();   // both CTAs' barriers exist before anyone arrives remotely
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem = bars->tmem_base;
 
@@ -134,42 +216,63 @@ q4k_prefill_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_consta
         if (lane == 0) {
             uint32_t issued = 0;
             for (uint32_t kb = 0; kb < n_kb && !bars->abort; ++kb, ++issued) {
-                const uint32_t s = kb % PF_A_STAGES, ph = (kb / PF_A_STAGES) & 1u;
+                const uint32_t s = kb % A_STAGES, ph = (kb / A_STAGES) & 1u;
                 if (!mbar_wait(&bars->a_empty[s], ph ^ 1u, status)) {
                     bars->abort = 1;
                     break;
                 }
-                mbar_expect_tx(&bars->a_full[s], halves * PF_A_HALF_BYTES);
+                mbar_expect_tx(&bars->a_full[s], halves * A_HALF_BYTES);
                 for (uint32_t h = 0; h < halves; ++h)
-                    tma_load_2d(base + s * PF_A_BYTES + h * PF_A_HALF_BYTES, &tm_a, (int32_t)(kb * 64u),
-                                (int32_t)(m0 + h * PF_TOK), &bars->a_full[s]);
+                    tma_load_2d(base + s * A_BYTES + h * A_HALF_BYTES, &tm_a, (int32_t)(kb * 64u),
+                                (int32_t)(m0 + h * PF_TOK + (PAIR ? rank * 128u : 0u)), &bars->a_full[s]);
             }
             // nothing may still be in flight towards this CTA's shared memory at exit
-            for (uint32_t j = issued > PF_A_STAGES ? issued - PF_A_STAGES : 0; j < issued; ++j)
-                (void)mbar_wait(&bars->a_full[j % PF_A_STAGES], (j / PF_A_STAGES) & 1u, status);
+            for (uint32_t j = issued > A_STAGES ? issued - A_STAGES : 0; j < issued; ++j)
+                (void)mbar_wait(&bars->a_full[j % A_STAGES], (j / A_STAGES) & 1u, status);
         }
     } else if (warp == 1) {
-        // ---------------- MMA issue ----------------
-        if (lane == 0) {
+        // ---------------- MMA issue (pair: the leader issues for both; the peer relays) ----------------
+        if (lane == 0 && (!PAIR || leader)) {
             bool ok = true;
             for (uint32_t kb = 0; kb < n_kb && ok && !bars->abort; ++kb) {
-                const uint32_t sa = kb % PF_A_STAGES, pa = (kb / PF_A_STAGES) & 1u;
+                const uint32_t sa = kb % A_STAGES, pa = (kb / A_STAGES) & 1u;
                 const uint32_t sw = kb % PF_W_STAGES, pw = (kb / PF_W_STAGES) & 1u;
-                ok = mbar_wait(&bars->a_full[sa], pa, status) && mbar_wait(&bars->w_full[sw], pw, status);
+                if constexpr (PAIR)
+                    ok = mbar_wait_cluster(&bars->a_full[sa], pa, status) && mbar_wait_cluster(&bars->w_full[sw], pw, status);
+                else
+                    ok = mbar_wait(&bars->a_full[sa], pa, status) && mbar_wait(&bars->w_full[sw], pw, status);
                 if (!ok) break;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 const uint64_t wd = sw128_desc(base + PF_OFF_W + sw * PF_W_BYTES);
                 for (uint32_t h = 0; h < halves; ++h) {
-                    const uint64_t ad = sw128_desc(base + sa * PF_A_BYTES + h * PF_A_HALF_BYTES);
+                    const uint64_t ad = sw128_desc(base + sa * A_BYTES + h * A_HALF_BYTES);
 #pragma unroll
-                    for (uint32_t kk = 0; kk < 4; ++kk)   // 16 bf16 = 32 bytes = 2 descriptor units per step
-                        umma_bf16(tmem + h * PF_TOK, wd + 2u * kk, ad + 2u * kk, (kb | kk) != 0u);
+                    for (uint32_t kk = 0; kk < 4; ++kk) {  // 16 bf16 = 32 bytes = 2 descriptor units per step
+                        if constexpr (PAIR) umma_bf16_pair(tmem + h * PF_TOK, wd + 2u * kk, ad + 2u * kk, (kb | kk) != 0u);
+                        else umma_bf16(tmem + h * PF_TOK, wd + 2u * kk, ad + 2u * kk, (kb | kk) != 0u);
+                    }
                 }
-                umma_commit(&bars->a_empty[sa]);   // both fire when the MMAs above have read their operands
-                umma_commit(&bars->w_empty[sw]);
+                if constexpr (PAIR) {
+                    umma_commit_pair(&bars->a_empty[sa]);   // frees the stages in both CTAs
+                    umma_commit_pair(&bars->w_empty[sw]);
+                } else {
+                    umma_commit(&bars->a_empty[sa]);   // both fire when the MMAs above have read their operands
+                    umma_commit(&bars->w_empty[sw]);
+                }
             }
             if (!ok) bars->abort = 1;
-            umma_commit(&bars->acc_full);          // accumulators complete (or nothing outstanding)
+            if constexpr (PAIR) umma_commit_pair(&bars->acc_full);
+            else umma_commit(&bars->acc_full);     // accumulators complete (or nothing outstanding)
+        } else if (PAIR && lane == 0) {
+            // peer: tell the leader when this CTA's share of the token tile has landed
+            for (uint32_t kb = 0; kb < n_kb && !bars->abort; ++kb) {
+                const uint32_t sa = kb % A_STAGES, pa = (kb / A_STAGES) & 1u;
+                if (!mbar_wait(&bars->a_full[sa], pa, status)) {
+                    bars->abort = 1;
+                    break;
+                }
+                mbar_arrive_remote(&bars->a_full[sa], 0u);
+            }
         }
     } else if (warp == 2) {
         // ---------------- raw superblocks: 128 rows x 144 bytes per superblock column ----------------
@@ -237,7 +340,10 @@ q4k_prefill_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_consta
                 *reinterpret_cast<uint4*>(wrow + (((5u + 2u * seg) ^ x7) << 4)) = make_uint4(hi[4], hi[5], hi[6], hi[7]);
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic writes -> async proxy (MMA)
                 __syncwarp();
-                if (lane == 0) mbar_arrive(&bars->w_full[sw]);
+                if (lane == 0) {
+                    if (PAIR && !leader) mbar_arrive_remote(&bars->w_full[sw], 0u);   // the leader's MMA thread waits
+                    else mbar_arrive(&bars->w_full[sw]);
+                }
             }
             if (!ok) break;
             __syncwarp();
@@ -283,9 +389,13 @@ q4k_prefill_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_consta
 
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
+    if constexpr (PAIR) cluster_sync_all();   // no remote arrive or multicast commit may still target a CTA that left
     if (warp == 2) {
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(512u) : "memory");
+        if constexpr (PAIR)
+            asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(512u) : "memory");
+        else
+            asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(512u) : "memory");
     }
 }
 
@@ -304,16 +414,19 @@ PFN_cuTensorMapEncodeTiled_v12000 encode_fn() {
 }  // namespace
 
 cudaError_t launch_q4k_prefill(const uint8_t* q, const uint16_t* a_bf16, float* c, uint32_t m_tokens,
-                               uint32_t n_rows, uint32_t n_sb, uint32_t* status, cudaStream_t stream) {
+                               uint32_t n_rows, uint32_t n_sb, uint32_t* status, cudaStream_t stream, int form) {
     if (m_tokens == 0 || n_rows == 0 || n_sb == 0) return cudaSuccess;
     auto encode = encode_fn();
     if (!encode) return cudaErrorNotSupported;
+    const uint32_t tiles = (n_rows + PF_ROWS - 1) / PF_ROWS;
+    const bool pair = form != 1 && tiles >= 2;   // form: 0 = choose, 1 = single CTA, 2 = CTA pair
     const uint64_t k = (uint64_t)n_sb * Q4K_SB_ELEMS;
     CUtensorMap tm_a, tm_w;
-    {   // tokens: [m_tokens][k] bf16, box = 64 k x 256 tokens, 128-byte swizzle; rows past the end read as zero
+    {   // tokens: [m_tokens][k] bf16, box = 64 k x 256 (pair: 128) tokens, 128-byte swizzle; rows past
+        // the end read as zero
         cuuint64_t dims[2] = {k, m_tokens};
         cuuint64_t strides[1] = {k * 2};
-        cuuint32_t box[2] = {64, PF_TOK};
+        cuuint32_t box[2] = {64, pair ? 128u : PF_TOK};
         cuuint32_t estr[2] = {1, 1};
         if (encode(&tm_a, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<uint16_t*>(a_bf16), dims, strides, box, estr,
                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
@@ -330,11 +443,19 @@ cudaError_t launch_q4k_prefill(const uint8_t* q, const uint16_t* a_bf16, float* 
                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
             return cudaErrorInvalidValue;
     }
-    cudaError_t e = cudaFuncSetAttribute(q4k_prefill_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)PF_SMEM);
+    auto kern = pair ? q4k_prefill_kernel<true> : q4k_prefill_kernel<false>;
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)PF_SMEM);
     if (e != cudaSuccess) return e;
-    dim3 grid((n_rows + PF_ROWS - 1) / PF_ROWS, (m_tokens + PF_TOK_MAX - 1) / PF_TOK_MAX);
-    q4k_prefill_kernel<<<grid, PF_THREADS, PF_SMEM, stream>>>(tm_a, tm_w, c, m_tokens, n_rows, n_sb, status);
-    return cudaGetLastError();
+    cudaLaunchConfig_t cfg{};
+    // pair: an even number of CTAs; a trailing CTA without rows of its own still holds its share of the tokens
+    cfg.gridDim = dim3(pair ? (tiles + 1u) & ~1u : tiles, (m_tokens + PF_TOK_MAX - 1) / PF_TOK_MAX);
+    cfg.blockDim = dim3(PF_THREADS);
+    cfg.dynamicSmemBytes = PF_SMEM, cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2, attr[0].val.clusterDim.y = 1, attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr, cfg.numAttrs = pair ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kern, tm_a, tm_w, c, m_tokens, n_rows, n_sb, status);
 }
 
 }  // namespace axc

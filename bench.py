@@ -603,7 +603,7 @@ def run_prefill(args):
 
     def step():
         for j in range(n_mat):
-            ops.q4k_prefill(weights[j], a_dev, m, n, n_sb, c=outs[j], status=status)
+            ops.q4k_prefill(weights[j], a_dev, m, n, n_sb, c=outs[j], status=status, form=args.prefill_form)
 
     step()
     torch.cuda.synchronize()
@@ -644,7 +644,7 @@ def run_prefill(args):
         "steps": steps, "warmup": warmup, "ms_per_step": round(ms, 5), "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
         "config": {"workload": "Q4_K_M batched prefill, M=512 tokens, K=4096, N=14336, bf16 operands, fp32 accumulate",
-                   "calls_per_step": n_mat, "launch": "stream",
+                   "calls_per_step": n_mat, "launch": "stream", "form": args.prefill_form,
                    "l2": f"{n_mat} distinct weight matrices and outputs per step (0.5 GB) visited round-robin"},
         "us_per_call": round(ms * 1e3 / n_mat, 3),
         "roofline": {"bound": "tensor", "achieved": round(tf, 2), "peak": peak, "unit": "TFLOP/s",
@@ -660,6 +660,8 @@ def main():
     ap.add_argument("--workload", choices=["matvec", "decode70b", "prefill"], default="matvec",
                     help="matvec: the headline 14336 x 4096 metric; decode70b: the 70B-shaped decode sweep")
     ap.add_argument("--layers", type=int, default=80, help="decode70b: layers in the stack")
+    ap.add_argument("--prefill-form", type=int, default=0, choices=[0, 1, 2],
+                    help="prefill: 0 = library's choice, 1 = one CTA per tile, 2 = CTA pair (cta_group::2)")
     ap.add_argument("--decode-mode", choices=["auto", "prepared", "fused", "poll"], default="auto",
                     help="decode70b: how a linear's output reaches the next linear (see decode.py)")
     ap.add_argument("--gpus", type=int, default=1)

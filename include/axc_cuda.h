@@ -272,6 +272,10 @@ int axc_cuda_q4k_matvec_allgather(const void* q, const float* x, uint32_t rows_l
  * bounded wait inside the kernel ran out. */
 int axc_cuda_q4k_prefill(const void* q, const uint16_t* a_bf16, float* c, uint32_t m_tokens,
                          uint32_t n_rows, uint32_t n_superblocks, void* stream, uint32_t* status);
+/* The same with the kernel form chosen by the caller: 0 = the library's choice, 1 = one CTA per
+ * 128-row tile (tcgen05.mma.cta_group::1), 2 = a pair of CTAs per 256 rows (cta_group::2). */
+int axc_cuda_q4k_prefill_form(const void* q, const uint16_t* a_bf16, float* c, uint32_t m_tokens,
+                              uint32_t n_rows, uint32_t n_superblocks, void* stream, uint32_t* status, int form);
 
 /* Q4_K_M matvec whose activations are assembled inside the kernel: x = a [+ b], where a and b
  * are each a plain fp32 vector (x, x2) or a vector of (value, epoch) words that the all-gather

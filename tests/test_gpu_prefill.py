@@ -20,11 +20,11 @@ def bf16_operands(m, k, seed):
     return a_bf, a_bf.to(torch.float32).numpy()
 
 
-def check(ops, synth, m, n, n_sb, seed):
+def check(ops, synth, m, n, n_sb, seed, form=0):
     q = synth.q4k_weights(n, n_sb, seed)
     a_bf, a32 = bf16_operands(m, n_sb * 256, seed + 1)
     st = ops.new_status()
-    c = ops.q4k_prefill(torch.from_numpy(q).cuda(), a_bf.cuda(), m, n, n_sb, status=st)
+    c = ops.q4k_prefill(torch.from_numpy(q).cuda(), a_bf.cuda(), m, n, n_sb, status=st, form=form)
     torch.cuda.synchronize()
     assert int(st.item()) == 0
     ref = oracle.q4km_prefill(q, a32, m, n, n_sb)
@@ -38,9 +38,20 @@ def check(ops, synth, m, n, n_sb, seed):
 
 
 @pytest.mark.parametrize("m,n,n_sb", [(64, 128, 1), (256, 128, 2), (512, 256, 4), (300, 200, 2),
-                                      (1, 128, 1), (17, 130, 3), (600, 384, 2), (1030, 128, 1)])
-def test_prefill_matches_oracle(ops, synth, m, n, n_sb):
-    check(ops, synth, m, n, n_sb, 9000 + m + n + n_sb)
+                                      (1, 128, 1), (17, 130, 3), (600, 384, 2), (1030, 128, 1), (130, 384, 1)])
+@pytest.mark.parametrize("form", [1, 2])
+def test_prefill_matches_oracle(ops, synth, m, n, n_sb, form):
+    """form 1: one CTA per tile; form 2: CTA pairs (a 128-row matrix has one tile and runs as form 1)."""
+    check(ops, synth, m, n, n_sb, 9000 + m + n + n_sb, form)
+
+
+def test_prefill_forms_agree_bit_for_bit(ops, synth):
+    """Both forms accumulate the same products in the same k order."""
+    m, n, n_sb = 300, 640, 3
+    q = torch.from_numpy(synth.q4k_weights(n, n_sb, 9050)).cuda()
+    a_bf, _ = bf16_operands(m, n_sb * 256, 9051)
+    a = a_bf.cuda()
+    assert torch.equal(ops.q4k_prefill(q, a, m, n, n_sb, form=1), ops.q4k_prefill(q, a, m, n, n_sb, form=2))
 
 
 def test_prefill_weights_are_the_bit_exact_bf16_dequant(ops, synth):
