@@ -37,13 +37,13 @@ namespace {
 constexpr uint32_t PF_ROWS = 128;                 // weight rows per CTA = MMA M
 constexpr uint32_t PF_TOK = 256;                  // tokens per MMA = MMA N
 constexpr uint32_t PF_TOK_MAX = 512;              // tokens per CTA (all of tensor memory)
-constexpr uint32_t PF_W_STAGES = 3, PF_RAW_STAGES = 2;
-constexpr uint32_t PF_A_REGION = 131072;                      // token stages: 2 x 64 KB (single) or 4 x 32 KB (pair)
-constexpr uint32_t PF_MAX_A_STAGES = 4;
+constexpr uint32_t PF_RAW_STAGES = 2;
+// Token stages + operand-tile stages share 176 KB: single 2 x 64 KB + 3 x 16 KB; pair 3 x 32 KB +
+// 5 x 16 KB (the pair's stage hand-offs cross between two SMs and need the deeper operand ring).
+constexpr uint32_t PF_MAX_A_STAGES = 4, PF_MAX_W_STAGES = 5;
 constexpr uint32_t PF_W_BYTES = PF_ROWS * 128;                // 128 rows x 64 bf16
 constexpr uint32_t PF_RAW_BYTES = PF_ROWS * Q4K_SB_BYTES;     // 18432
-constexpr uint32_t PF_OFF_W = PF_A_REGION;                                     // 131072
-constexpr uint32_t PF_OFF_RAW = PF_OFF_W + PF_W_STAGES * PF_W_BYTES;           // 180224
+constexpr uint32_t PF_OFF_RAW = 180224;
 constexpr uint32_t PF_OFF_BAR = PF_OFF_RAW + PF_RAW_STAGES * PF_RAW_BYTES;     // 217088
 constexpr uint32_t PF_SMEM = PF_OFF_BAR + 256 + 1024;                          // + alignment slack
 constexpr uint32_t PF_DEQ_WARPS = 8;
@@ -106,7 +106,7 @@ __device__ __forceinline__ void mbar_arrive_remote(uint64_t* bar, uint32_t cta) 
     asm volatile(
         "{\n\t.reg .b32 r;\n\t"
         "mapa.shared::cluster.u32 r, %0, %1;\n\t"
-        "mbarrier.arrive.release.cluster.shared::cluster.b64 _, [r];\n\t}" ::"r"(smem_u32(bar)),
+        "mbarrier.arrive.shared::cluster.b64 _, [r];\n\t}" ::"r"(smem_u32(bar)),
         "r"(cta)
         : "memory");
 }
@@ -118,7 +118,7 @@ __device__ __forceinline__ bool mbar_wait_cluster(uint64_t* bar, uint32_t parity
         uint32_t done;
         asm volatile(
             "{\n\t.reg .pred p;\n\t"
-            "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
             "selp.u32 %0, 1, 0, p;\n\t}"
             : "=r"(done)
             : "r"(addr), "r"(parity)
@@ -146,7 +146,7 @@ __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
 
 struct PfBars {
     uint64_t a_full[PF_MAX_A_STAGES], a_empty[PF_MAX_A_STAGES];
-    uint64_t w_full[PF_W_STAGES], w_empty[PF_W_STAGES];
+    uint64_t w_full[PF_MAX_W_STAGES], w_empty[PF_MAX_W_STAGES];
     uint64_t raw_full[PF_RAW_STAGES], raw_empty[PF_RAW_STAGES];
     uint64_t acc_full;
     uint32_t tmem_base;
@@ -171,7 +171,10 @@ q4k_prefill_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_consta
     const uint32_t n_kb = n_sb * 4;
     // Pair form: CTA `rank` of the cluster holds tokens [rank * 128, rank * 128 + 128) of every
     // 256-token block; rank 0 (the leader) issues the MMAs.
-    constexpr uint32_t A_STAGES = PAIR ? 4u : 2u;
+    constexpr uint32_t A_STAGES = PAIR ? 3u : 2u;
+    constexpr uint32_t PF_W_STAGES = PAIR ? 5u : 3u;
+    constexpr uint32_t PF_OFF_W = PAIR ? 3u * 32768u : 2u * 65536u;
+    static_assert(PF_OFF_W + PF_W_STAGES * PF_W_BYTES == PF_OFF_RAW, "token and operand stages fill the region below the raw tiles");
     constexpr uint32_t A_HALF_BYTES = PAIR ? 128u * 128u : PF_TOK * 128u;   // one block's share per CTA
     constexpr uint32_t A_BYTES = 2u * A_HALF_BYTES;
     uint32_t rank = 0;
