@@ -119,7 +119,8 @@ SYMBOLS = {
     "axc_cuda_q4k_matvec_allgather": (C.c_int, [_VP, _VP, C.c_uint32, C.c_uint32, C.POINTER(AxcGather), _VP, _VP,
                                                 C.POINTER(AxcTuning)]),
     "axc_cuda_q4k_prefill": (C.c_int, [_VP, _VP, _VP, C.c_uint32, C.c_uint32, C.c_uint32, _VP, _VP]),
-    "axc_cuda_q4k_prefill_form": (C.c_int, [_VP, _VP, _VP, C.c_uint32, C.c_uint32, C.c_uint32, _VP, _VP, C.c_int]),
+    "axc_cuda_q4k_prefill_form": (C.c_int, [_VP, _VP, _VP, C.c_uint32, C.c_uint32, C.c_uint32, _VP, _VP, C.c_int,
+                                            C.c_uint32]),
     "axc_cuda_q4k_matvec_fused": (C.c_int, [_VP, C.POINTER(AxcXSrc), _VP, C.c_uint32, C.c_uint32,
                                             C.POINTER(AxcGather), _VP, _VP, C.POINTER(AxcTuning)]),
     "axc_cuda_q4k_prepared_x_bytes": (C.c_size_t, [C.c_uint32]),

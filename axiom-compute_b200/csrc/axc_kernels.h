@@ -65,7 +65,8 @@ cudaError_t launch_q4k_dequant(const uint8_t* q, float* w, uint32_t rows, uint32
 // bf16, W [n_rows][n_sb] Q4_K_M superblocks, C [m_tokens][n_rows] fp32.
 cudaError_t launch_q4k_prefill(const uint8_t* q, const uint16_t* a_bf16, float* c, uint32_t m_tokens,
                                uint32_t n_rows, uint32_t n_sb, uint32_t* status, cudaStream_t stream,
-                               int form = 0 /* 0 choose, 1 single CTA per tile, 2 CTA pair */);
+                               int form = 0 /* 0 choose, 1 single CTA per tile, 2 CTA pair */,
+                               bool independent = false /* inputs / C untouched by the launch before */);
 
 cudaError_t launch_gather_finish(const uint64_t* pairs, const uint32_t* epoch_ptr, float* out, uint32_t n,
                                  uint32_t* status, cudaStream_t stream, bool overlap);

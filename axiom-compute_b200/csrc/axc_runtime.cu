@@ -810,11 +810,12 @@ int axc_cuda_q4k_matvec_allgather(const void* q, const float* x, uint32_t rows_l
 
 int axc_cuda_q4k_prefill(const void* q, const uint16_t* a_bf16, float* c, uint32_t m_tokens,
                          uint32_t n_rows, uint32_t n_superblocks, void* stream, uint32_t* status) {
-    return axc_cuda_q4k_prefill_form(q, a_bf16, c, m_tokens, n_rows, n_superblocks, stream, status, 0);
+    return axc_cuda_q4k_prefill_form(q, a_bf16, c, m_tokens, n_rows, n_superblocks, stream, status, 0, 0);
 }
 
 int axc_cuda_q4k_prefill_form(const void* q, const uint16_t* a_bf16, float* c, uint32_t m_tokens,
-                              uint32_t n_rows, uint32_t n_superblocks, void* stream, uint32_t* status, int form) {
+                              uint32_t n_rows, uint32_t n_superblocks, void* stream, uint32_t* status, int form,
+                              uint32_t flags) {
     clear_error();
     if (form < 0 || form > 2) return fail(AXC_ERR_INVALID_ARGUMENT, "prefill form must be 0 (choose), 1 (single CTA) or 2 (CTA pair)");
     if (m_tokens == 0 || n_rows == 0) return AXC_OK;
@@ -823,7 +824,7 @@ int axc_cuda_q4k_prefill_form(const void* q, const uint16_t* a_bf16, float* c, u
     if (rc != AXC_OK) return rc;
     if ((uint64_t)n_superblocks * 144u >= (1ull << 32) || (uint64_t)m_tokens * n_rows >= (1ull << 40))
         return fail(AXC_ERR_INVALID_ARGUMENT, "prefill shape out of range");
-    cudaError_t e = axc::launch_q4k_prefill((const uint8_t*)q, a_bf16, c, m_tokens, n_rows, n_superblocks, status, (cudaStream_t)stream, form);
+    cudaError_t e = axc::launch_q4k_prefill((const uint8_t*)q, a_bf16, c, m_tokens, n_rows, n_superblocks, status, (cudaStream_t)stream, form, (flags & AXC_PREFILL_INDEPENDENT) != 0);
     if (e == cudaErrorNotSupported)
         return fail(AXC_ERR_PIPELINE_CREATION_FAILED, "pipeline creation failed: the driver does not provide cuTensorMapEncodeTiled");
     if (e == cudaErrorInvalidValue)

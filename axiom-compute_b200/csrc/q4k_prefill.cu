@@ -156,7 +156,13 @@ struct PfBars {
 template <bool PAIR>
 __global__ void __launch_bounds__(PF_THREADS, 1)
 q4k_prefill_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_w,
-                   float* __restrict__ c, uint32_t m_total, uint32_t n_rows, uint32_t n_sb, uint32_t* status) {
+                   float* __restrict__ c, uint32_t m_total, uint32_t n_rows, uint32_t n_sb, uint32_t* status,
+                   uint32_t independent) {
+    // Programmatic dependent launch: the next launch may be scheduled onto SMs this grid leaves
+    // idle (112 CTAs on 148 SMs).  Unless the caller declared this call independent of the one
+    // before it (inputs not produced, C not read by it), nothing is read before that call is done.
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    if (!independent) asm volatile("griddepcontrol.wait;" ::: "memory");
     extern __shared__ uint8_t smem_dyn[];
     const uint32_t raw_addr = smem_u32(smem_dyn);
     const uint32_t base = (raw_addr + 1023u) & ~1023u;   // the swizzled tiles need 1024-byte alignment
@@ -357,6 +363,7 @@ q4k_prefill_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_consta
         // ---------------- epilogue: TMEM lane = weight row, column = token ----------------
         ok = __all_sync(0xFFFFFFFFu, mbar_wait(&bars->acc_full, 0u, status) && !bars->abort);
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        if (independent) asm volatile("griddepcontrol.wait;" ::: "memory");   // stream order for the stores of C
         if (ok) {
             const uint32_t quad = warp & 3u;             // the TMEM lanes this warp may read
             const uint32_t col_half = dw / 4u;           // warps 3..6: tokens 0..255, warps 7..10: 256..511
@@ -417,7 +424,8 @@ PFN_cuTensorMapEncodeTiled_v12000 encode_fn() {
 }  // namespace
 
 cudaError_t launch_q4k_prefill(const uint8_t* q, const uint16_t* a_bf16, float* c, uint32_t m_tokens,
-                               uint32_t n_rows, uint32_t n_sb, uint32_t* status, cudaStream_t stream, int form) {
+                               uint32_t n_rows, uint32_t n_sb, uint32_t* status, cudaStream_t stream, int form,
+                               bool independent) {
     if (m_tokens == 0 || n_rows == 0 || n_sb == 0) return cudaSuccess;
     auto encode = encode_fn();
     if (!encode) return cudaErrorNotSupported;
@@ -454,11 +462,13 @@ cudaError_t launch_q4k_prefill(const uint8_t* q, const uint16_t* a_bf16, float* 
     cfg.gridDim = dim3(pair ? (tiles + 1u) & ~1u : tiles, (m_tokens + PF_TOK_MAX - 1) / PF_TOK_MAX);
     cfg.blockDim = dim3(PF_THREADS);
     cfg.dynamicSmemBytes = PF_SMEM, cfg.stream = stream;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeClusterDimension;
-    attr[0].val.clusterDim.x = 2, attr[0].val.clusterDim.y = 1, attr[0].val.clusterDim.z = 1;
-    cfg.attrs = attr, cfg.numAttrs = pair ? 1 : 0;
-    return cudaLaunchKernelEx(&cfg, kern, tm_a, tm_w, c, m_tokens, n_rows, n_sb, status);
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    attr[1].id = cudaLaunchAttributeClusterDimension;
+    attr[1].val.clusterDim.x = 2, attr[1].val.clusterDim.y = 1, attr[1].val.clusterDim.z = 1;
+    cfg.attrs = attr, cfg.numAttrs = pair ? 2 : 1;
+    return cudaLaunchKernelEx(&cfg, kern, tm_a, tm_w, c, m_tokens, n_rows, n_sb, status, independent ? 1u : 0u);
 }
 
 }  // namespace axc

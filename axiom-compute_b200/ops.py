@@ -127,10 +127,12 @@ def q4k_matvec_plan(rows: int, n_superblocks: int, tuning=None, sm_count: int = 
 
 
 def q4k_prefill(q: torch.Tensor, a_bf16: torch.Tensor, m_tokens: int, n_rows: int, n_superblocks: int,
-                c: Optional[torch.Tensor] = None, status: Optional[torch.Tensor] = None, form: int = 0) -> torch.Tensor:
+                c: Optional[torch.Tensor] = None, status: Optional[torch.Tensor] = None, form: int = 0,
+                independent: bool = False) -> torch.Tensor:
     """C[m, n] = sum_k A[m, k] * bf16(W[n, k]) on the tensor cores (tcgen05); A is a bf16 tensor of
     shape (m_tokens, n_superblocks * 256), the result fp32 of shape (m_tokens, n_rows).  `form`:
-    0 = the library's choice, 1 = one CTA per tile, 2 = a CTA pair per 256 rows."""
+    0 = the library's choice, 1 = one CTA per tile, 2 = a CTA pair per 256 rows.  `independent`: q and a
+    are not written and c not touched by the launch directly before (lets the call overlap it)."""
     qp = _chk(q, torch.uint8, "q", n_rows * n_superblocks * Q4K_SB_BYTES)
     ap = _chk(a_bf16, torch.bfloat16, "a", m_tokens * n_superblocks * Q4K_SB_ELEMS)
     if c is None:
@@ -138,6 +140,7 @@ def q4k_prefill(q: torch.Tensor, a_bf16: torch.Tensor, m_tokens: int, n_rows: in
     cp = _chk(c, torch.float32, "c", m_tokens * n_rows)
     with torch.cuda.device(q.device):
         rc = _ffi.lib().axc_cuda_q4k_prefill_form(qp, ap, cp, m_tokens, n_rows, n_superblocks, _stream_ptr(),
-                                                  status.data_ptr() if status is not None else None, int(form))
+                                                  status.data_ptr() if status is not None else None, int(form),
+                                                  1 if independent else 0)
     _raise_for(rc)
     return c

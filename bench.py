@@ -601,9 +601,13 @@ def run_prefill(args):
     outs = [torch.empty((m, n), dtype=torch.float32, device=dev) for _ in range(n_mat)]
     status = ops.new_status(dev)
 
-    def step():
+    indep = not args.prefill_strict   # the 8 calls of a step share A and write 8 different C
+
+    def step(independent=None):
+        ind = indep if independent is None else independent
         for j in range(n_mat):
-            ops.q4k_prefill(weights[j], a_dev, m, n, n_sb, c=outs[j], status=status, form=args.prefill_form)
+            ops.q4k_prefill(weights[j], a_dev, m, n, n_sb, c=outs[j], status=status, form=args.prefill_form,
+                            independent=ind)
 
     step()
     torch.cuda.synchronize()
@@ -631,6 +635,21 @@ def run_prefill(args):
     torch.cuda.synchronize()
     sampler.stop()
     ms = e0.elapsed_time(e1) / steps
+    strict = None
+    if indep:   # the same step with every call ordered after the one before, for reference
+        for _ in range(3):
+            step(False)
+        torch.cuda.synchronize()
+        s_steps = max(1, min(steps, 100))
+        e0.record()
+        for _ in range(s_steps):
+            step(False)
+        e1.record()
+        torch.cuda.synchronize()
+        ms_strict = e0.elapsed_time(e1) / s_steps
+        strict = {"us_per_call": round(ms_strict * 1e3 / n_mat, 3),
+                  "value": round(2.0 * m * n * n_sb * 256 * n_mat / (ms_strict * 1e-3) / 1e12, 2), "unit": "TFLOP/s",
+                  "steps": s_steps}
     flops = 2.0 * m * n * n_sb * 256
     tf = flops * n_mat / (ms * 1e-3) / 1e12
     try:
@@ -645,8 +664,9 @@ def run_prefill(args):
         "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
         "config": {"workload": "Q4_K_M batched prefill, M=512 tokens, K=4096, N=14336, bf16 operands, fp32 accumulate",
                    "calls_per_step": n_mat, "launch": "stream", "form": args.prefill_form,
+                   "launch_dependency": "independent calls (shared A, distinct C)" if indep else "strict stream order",
                    "l2": f"{n_mat} distinct weight matrices and outputs per step (0.5 GB) visited round-robin"},
-        "us_per_call": round(ms * 1e3 / n_mat, 3),
+        "us_per_call": round(ms * 1e3 / n_mat, 3), "strict_stream_order": strict,
         "roofline": {"bound": "tensor", "achieved": round(tf, 2), "peak": peak, "unit": "TFLOP/s",
                      "frac": round(tf / peak, 4), "traffic": None, "kernel": "q4k_prefill_kernel",
                      "flops_per_launch": flops, "peak_source": peak_src},
@@ -662,6 +682,8 @@ def main():
     ap.add_argument("--layers", type=int, default=80, help="decode70b: layers in the stack")
     ap.add_argument("--prefill-form", type=int, default=0, choices=[0, 1, 2],
                     help="prefill: 0 = library's choice, 1 = one CTA per tile, 2 = CTA pair (cta_group::2)")
+    ap.add_argument("--prefill-strict", action="store_true",
+                    help="prefill: every call ordered after the one before (no overlap onto idle SMs)")
     ap.add_argument("--decode-mode", choices=["auto", "prepared", "fused", "poll"], default="auto",
                     help="decode70b: how a linear's output reaches the next linear (see decode.py)")
     ap.add_argument("--gpus", type=int, default=1)

@@ -273,9 +273,15 @@ int axc_cuda_q4k_matvec_allgather(const void* q, const float* x, uint32_t rows_l
 int axc_cuda_q4k_prefill(const void* q, const uint16_t* a_bf16, float* c, uint32_t m_tokens,
                          uint32_t n_rows, uint32_t n_superblocks, void* stream, uint32_t* status);
 /* The same with the kernel form chosen by the caller: 0 = the library's choice, 1 = one CTA per
- * 128-row tile (tcgen05.mma.cta_group::1), 2 = a pair of CTAs per 256 rows (cta_group::2). */
+ * 128-row tile (tcgen05.mma.cta_group::1), 2 = a pair of CTAs per 256 rows (cta_group::2).
+ * flags: AXC_PREFILL_INDEPENDENT = the caller states that q and a are not written, and c not read
+ * or written, by the launch directly before this one in the stream (say the up projection right
+ * after the gate projection of the same activations): the call may then start on SMs the previous
+ * call leaves idle (a 14336-row matrix is 112 tiles on 148 SMs); only its stores of c wait. */
+#define AXC_PREFILL_INDEPENDENT 1u
 int axc_cuda_q4k_prefill_form(const void* q, const uint16_t* a_bf16, float* c, uint32_t m_tokens,
-                              uint32_t n_rows, uint32_t n_superblocks, void* stream, uint32_t* status, int form);
+                              uint32_t n_rows, uint32_t n_superblocks, void* stream, uint32_t* status, int form,
+                              uint32_t flags);
 
 /* Q4_K_M matvec whose activations are assembled inside the kernel: x = a [+ b], where a and b
  * are each a plain fp32 vector (x, x2) or a vector of (value, epoch) words that the all-gather

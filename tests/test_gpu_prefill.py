@@ -92,3 +92,23 @@ def test_prefill_full_shape_linearity(ops, synth):
     rms = np.sqrt(np.mean(ref.astype(np.float64) ** 2))
     assert (np.abs(got - ref) <= 1e-2 * np.maximum(np.abs(ref), rms)).all()
     assert np.abs(got - ref).max() <= 1e-4 * rms
+
+
+def test_prefill_independent_calls_back_to_back(ops, synth):
+    """Calls declared independent of the launch before them may overlap it on idle SMs; every C
+    is still exactly what the strictly ordered call produces."""
+    m, n, n_sb = 200, 384, 2
+    a_bf, _ = bf16_operands(m, n_sb * 256, 9400)
+    a = a_bf.cuda()
+    qs = [torch.from_numpy(synth.q4k_weights(n, n_sb, 9401 + j)).cuda() for j in range(4)]
+    ref = [ops.q4k_prefill(q, a, m, n, n_sb) for q in qs]
+    torch.cuda.synchronize()
+    st = ops.new_status()
+    outs = [torch.zeros((m, n), device="cuda") for _ in qs]
+    for _ in range(3):
+        for q, c in zip(qs, outs):
+            ops.q4k_prefill(q, a, m, n, n_sb, c=c, status=st, independent=True)
+    torch.cuda.synchronize()
+    assert int(st.item()) == 0
+    for r, c in zip(ref, outs):
+        assert torch.equal(r, c)
