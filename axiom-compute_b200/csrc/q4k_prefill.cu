@@ -308,7 +308,7 @@ q4k_prefill_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_consta
         bool ok = true;
         for (uint32_t sb = 0; sb < n_sb && ok; ++sb) {
             const uint32_t sr = sb % PF_RAW_STAGES, pr = (sb / PF_RAW_STAGES) & 1u;
-            // every verdict is made warp-uniform: the code below has warp-wide barriers and loads
+            // every outcome of a wait is made warp-uniform: the code below has warp-wide barriers and loads
             ok = __all_sync(0xFFFFFFFFu, mbar_wait(&bars->raw_full[sr], pr, status) && !bars->abort);
             if (!ok) break;
             const uint8_t* blk = sm + PF_OFF_RAW + sr * PF_RAW_BYTES + row * Q4K_SB_BYTES;
