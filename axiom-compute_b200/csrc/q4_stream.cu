@@ -640,9 +640,16 @@ static cudaError_t launch_stream(const uint8_t* q, const float* x, float* y, uin
     if (warps > 16) return cudaErrorInvalidConfiguration;
     p.rows_per_pass = (uint32_t)rows_per_pass;
     const int max_resident = 16 / warps > 0 ? 16 / warps : 1;
-    int ctas_per_sm = tune.ctas_per_sm > 0 ? tune.ctas_per_sm : max_resident;
+    // Calls declared independent of the launch before them (pdl 3) overlap it on every SM: one
+    // CTA per SM per launch, shared memory cut for two residents, so an SM always holds one CTA
+    // of this launch and one of the next and the per-CTA prologue (x staging) is paid once per
+    // SM per launch instead of twice.  Ordered launches cannot overlap: they fill the SM themselves.
+    const bool overlap_launches = tune.pdl == 3 && !tune.x_prepared;
+    int ctas_per_sm = tune.ctas_per_sm > 0 ? tune.ctas_per_sm : (overlap_launches ? 1 : max_resident);
     if (ctas_per_sm > 16) ctas_per_sm = 16;
-    int resident = tune.resident > 0 ? tune.resident : (ctas_per_sm < max_resident ? ctas_per_sm : max_resident);
+    int resident = tune.resident > 0 ? tune.resident
+                   : overlap_launches ? max_resident
+                                      : (ctas_per_sm < max_resident ? ctas_per_sm : max_resident);
     if (resident > max_resident) resident = max_resident;
 
     uint32_t grid = (uint32_t)(sm_count * ctas_per_sm);
