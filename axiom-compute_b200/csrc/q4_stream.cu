@@ -632,7 +632,14 @@ static cudaError_t launch_stream(const uint8_t* q, const float* x, float* y, uin
     // CTA shape: whole rows per pass, about `threads` threads.  `ctas_per_sm` sizes the grid,
     // `resident` the shared-memory budget (how many CTAs should fit on an SM together; about 120
     // registers per thread allow 16 warps per SM in total).
+    // Calls declared independent of the launch before them (pdl 3) overlap it on every SM: one
+    // small CTA per SM per launch (two rows per pass) and shared memory cut for up to four
+    // residents, so an SM holds CTAs of up to four consecutive launches and the per-CTA prologue
+    // (x staging) is paid once per SM per launch.  Ordered launches cannot overlap: they fill the
+    // SM themselves with larger CTAs.
+    const bool overlap_launches = tune.pdl == 3 && !tune.x_prepared;
     int threads = tune.threads > 0 ? tune.threads : 256;
+    if (tune.threads <= 0 && overlap_launches && p.warps_per_row <= 4) threads = 64 * (int)p.warps_per_row;
     if (p.warps_per_row > 8) threads = 512;
     int rows_per_pass = (threads / 32) / (int)p.warps_per_row;
     if (rows_per_pass < 1) rows_per_pass = 1;
@@ -640,15 +647,10 @@ static cudaError_t launch_stream(const uint8_t* q, const float* x, float* y, uin
     if (warps > 16) return cudaErrorInvalidConfiguration;
     p.rows_per_pass = (uint32_t)rows_per_pass;
     const int max_resident = 16 / warps > 0 ? 16 / warps : 1;
-    // Calls declared independent of the launch before them (pdl 3) overlap it on every SM: one
-    // CTA per SM per launch, shared memory cut for two residents, so an SM always holds one CTA
-    // of this launch and one of the next and the per-CTA prologue (x staging) is paid once per
-    // SM per launch instead of twice.  Ordered launches cannot overlap: they fill the SM themselves.
-    const bool overlap_launches = tune.pdl == 3 && !tune.x_prepared;
     int ctas_per_sm = tune.ctas_per_sm > 0 ? tune.ctas_per_sm : (overlap_launches ? 1 : max_resident);
     if (ctas_per_sm > 16) ctas_per_sm = 16;
     int resident = tune.resident > 0 ? tune.resident
-                   : overlap_launches ? max_resident
+                   : overlap_launches ? (max_resident < 4 ? max_resident : 4)
                                       : (ctas_per_sm < max_resident ? ctas_per_sm : max_resident);
     if (resident > max_resident) resident = max_resident;
 
