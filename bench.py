@@ -57,7 +57,7 @@ def measured_peak():
 
 # DRAM traffic of one streaming-kernel launch from an ncu capture of this workload
 # (dram__bytes_read.sum + dram__bytes_write.sum); see profiles/.  None until captured.
-NCU_TRAFFIC_BYTES_PER_LAUNCH = 33088256   # ncu: dram__bytes_read.sum 33 088 256 B + dram__bytes_write.sum 0 B (y stays in L2)
+NCU_TRAFFIC_BYTES_PER_LAUNCH = 33088512   # ncu: dram__bytes_read.sum 33 088 512 B + dram__bytes_write.sum 0 B (y stays in L2)
 
 
 class ClockSampler:
