@@ -211,7 +211,8 @@ typedef struct axc_tuning {
                             stream started before the dependency wait (default), 3 = as 2 and the
                             caller asserts that x is not written and y neither read nor written
                             by the previous launch on this stream: only the final store of y
-                            waits for that launch */
+                            waits for that launch, and the launch is shaped to overlap its
+                            neighbours (one small CTA per SM, up to four launches resident) */
     int32_t resident;    /* CTAs per SM the shared-memory budget is cut for; 0 = default */
 } axc_tuning;
 
