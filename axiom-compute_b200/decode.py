@@ -15,12 +15,14 @@ so a layer is four launches.  With more than one GPU every linear is row-sharded
 all-gather is fused into the producing kernel's epilogue.  How a linear's output becomes the
 next linear's input is the ``mode``:
 
-* ``"prepared"`` (default on one GPU): a small prepare kernel between the two (started while the producer is
+* ``"prepared"``: a small prepare kernel between the two (started while the producer is
   still running when the source is (value, epoch) words) assembles x once, quantises it to the
   digit-word image and leaves the sums of x^2; every CTA of the consumer reads its digit words
   straight into registers.
 * ``"fused"`` (default on several GPUs): every consumer CTA assembles and quantises x itself (``axc_cuda_q4k_matvec_fused``);
   with more than one GPU a finish kernel first unpacks the words into a plain vector.
+* ``"mixed"`` (default on one GPU): "prepared" for the linears with K > 8192 (the down projection),
+  "fused" for the others: the faster choice per shape.
 * ``"poll"``: as "fused", but every consumer CTA polls the (value, epoch) words itself (no launch in
   between, 2 x the bytes per CTA past L1: measured slower).
 
@@ -87,12 +89,12 @@ class DecodeSweep:
 
     def __init__(self, shape: SweepShape, device, seed: int = 0xA0C0 + 4 * 16, group=None, tuning=None,
                  mode: str = "auto"):
-        if mode == "auto":   # the faster one as measured: prepared on one GPU, fused + finish on several
+        if mode == "auto":   # the faster one as measured: mixed on one GPU, fused + finish on several
             multi = torch.distributed.is_available() and torch.distributed.is_initialized() \
                 and torch.distributed.get_world_size(group) > 1
-            mode = "fused" if multi else "prepared"
-        if mode not in ("prepared", "fused", "poll"):
-            raise ValueError("mode must be 'prepared', 'fused' or 'poll'")
+            mode = "fused" if multi else "mixed"
+        if mode not in ("prepared", "fused", "poll", "mixed"):
+            raise ValueError("mode must be 'prepared', 'fused', 'poll' or 'mixed'")
         self.shape, self.device = shape, torch.device(device)
         self.mode = mode
         self.consumer_polls = mode == "poll"
@@ -148,6 +150,12 @@ class DecodeSweep:
         self.vec = torch.zeros(words, dtype=torch.float32, device=self.device)
         if self.world == 1 and self.consumer_polls:
             raise ValueError("mode 'poll' needs more than one rank")
+        if self.world > 1 and self.mode == "mixed":
+            raise ValueError("mode 'mixed' is for one rank")
+        # per linear: hand x over through a prepare kernel?  mixed: only where K is large (measured per
+        # shape in strict order: 8192 x 28672 31.9 -> 28.2 us, but 8192 x 8192 11.0 -> 12.5 us)
+        self.prepared_linear = [self.mode == "prepared" or (self.mode == "mixed" and k > 8192)
+                                for _n, _r, k in shape.linears]
         k_max = max(k for _n, _r, k in shape.linears)
         img_bytes = int(_ffi.lib().axc_cuda_q4k_prepared_x_bytes(k_max // 256))
         self.images = [torch.zeros(img_bytes, dtype=torch.uint8, device=self.device) for _ in range(2)]
@@ -155,7 +163,7 @@ class DecodeSweep:
         if self.mode == "prepared":
             self.launches_per_token = 8 * shape.layers + (3 if self.world > 1 else 1)
         elif self.world == 1:
-            self.launches_per_token = 4 * shape.layers + 1
+            self.launches_per_token = (4 + sum(self.prepared_linear)) * shape.layers + 1
         elif self.consumer_polls:
             self.launches_per_token = 4 * shape.layers + 3
         else:
@@ -231,23 +239,22 @@ class DecodeSweep:
         with torch.cuda.device(self.device):
             if self.world > 1:
                 _raise_for(_ffi.lib().axc_cuda_gather_next_epoch(self.epoch.data_ptr(), self._stream()))
-            prepared = self.mode == "prepared"
             ov = self.world > 1      # epoch-word sources: the prepare kernel may start behind its producer
             for layer in range(sh.layers):
                 if layer == 0:
                     x = _ffi.AxcXSrc(self.h.data_ptr(), None, None, None, None, 1 if normalise_input else 0)
                 else:
                     x = self._src(layer - 1, 3)                         # h = unitRMS(d of the layer before)
-                if prepared:
-                    self._linear_prepared(layer, 0, x, normalise_input or layer > 0, ov and layer > 0)
-                    self._linear_prepared(layer, 1, self._src(layer, 0), True, ov)
-                    self._linear_prepared(layer, 2, self._src(layer, 1), True, ov)
-                    self._linear_prepared(layer, 3, self._src(layer, 2, 0, sh.ffn), True, ov)
-                    continue
-                self._linear(layer, 0, x)                               # q, k, v
-                self._linear(layer, 1, self._src(layer, 0))             # o = Wo . unitRMS(q): first `hidden` words
-                self._linear(layer, 2, self._src(layer, 1))             # g, u
-                self._linear(layer, 3, self._src(layer, 2, 0, sh.ffn))  # d = Wdown . unitRMS(g + u)
+                sources = (x,                                            # q, k, v = W h
+                           self._src(layer, 0),                          # o = Wo . unitRMS(q): first `hidden` words
+                           self._src(layer, 1),                          # g, u = W . unitRMS(o)
+                           self._src(layer, 2, 0, sh.ffn))               # d = Wdown . unitRMS(g + u)
+                for j, src in enumerate(sources):
+                    rms = normalise_input or layer > 0 or j > 0
+                    if self.prepared_linear[j]:
+                        self._linear_prepared(layer, j, src, rms, ov and (layer > 0 or j > 0))
+                    else:
+                        self._linear(layer, j, src)
             last = self.offsets[sh.layers - 1][3]
             if self.world > 1 and self.mode != "fused":
                 # nothing unpacked the words yet: every vector (k and v included) in one pass

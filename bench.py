@@ -684,7 +684,7 @@ def main():
                     help="prefill: 0 = library's choice, 1 = one CTA per tile, 2 = CTA pair (cta_group::2)")
     ap.add_argument("--prefill-strict", action="store_true",
                     help="prefill: every call ordered after the one before (no overlap onto idle SMs)")
-    ap.add_argument("--decode-mode", choices=["auto", "prepared", "fused", "poll"], default="auto",
+    ap.add_argument("--decode-mode", choices=["auto", "prepared", "fused", "poll", "mixed"], default="auto",
                     help="decode70b: how a linear's output reaches the next linear (see decode.py)")
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=2000)

@@ -164,13 +164,13 @@ def test_prepare_x_argument_checks(ffi, synth):
     assert L.axc_cuda_q4k_prepared_x_bytes(16) == 17 * 64 * 16 + 128
 
 
-@pytest.mark.parametrize("mode", ["prepared", "fused"])
+@pytest.mark.parametrize("mode", ["prepared", "fused", "mixed"])
 def test_decode_sweep_matches_oracle_on_a_small_stack(mode):
     decode = load_pkg("decode")
     shape = decode.SweepShape(hidden=512, kv=128, ffn=1024, layers=3)
-    assert decode.DecodeSweep(decode.SweepShape(256, 64, 256, 1), "cuda").mode == "prepared"   # auto, one GPU
+    assert decode.DecodeSweep(decode.SweepShape(256, 64, 256, 1), "cuda").mode == "mixed"   # auto, one GPU
     sweep = decode.DecodeSweep(shape, "cuda", seed=4242, mode=mode)
-    assert sweep.world == 1 and sweep.launches_per_token == (25 if mode == "prepared" else 13)
+    assert sweep.world == 1 and sweep.launches_per_token == {"prepared": 25, "fused": 13, "mixed": 13}[mode]
     rng = np.random.default_rng(5)
     h0 = rng.standard_normal(shape.hidden).astype(np.float32)
     weights = [tuple(w.cpu().numpy() for w in layer) for layer in sweep.weights]
