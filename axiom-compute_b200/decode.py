@@ -22,7 +22,9 @@ next linear's input is the ``mode``:
 * ``"fused"`` (default on several GPUs): every consumer CTA assembles and quantises x itself (``axc_cuda_q4k_matvec_fused``);
   with more than one GPU a finish kernel first unpacks the words into a plain vector.
 * ``"mixed"`` (default on one GPU): "prepared" for the linears with K > 8192 (the down projection),
-  "fused" for the others: the faster choice per shape.
+  "fused" for the others: the faster choice per shape on one GPU.  On several GPUs it runs (the
+  prepare kernel then polls the words of gate+up) but measured slower than "fused" (6.29 against
+  5.72 ms/token on two GPUs).
 * ``"poll"``: as "fused", but every consumer CTA polls the (value, epoch) words itself (no launch in
   between, 2 x the bytes per CTA past L1: measured slower).
 
@@ -150,12 +152,14 @@ class DecodeSweep:
         self.vec = torch.zeros(words, dtype=torch.float32, device=self.device)
         if self.world == 1 and self.consumer_polls:
             raise ValueError("mode 'poll' needs more than one rank")
-        if self.world > 1 and self.mode == "mixed":
-            raise ValueError("mode 'mixed' is for one rank")
         # per linear: hand x over through a prepare kernel?  mixed: only where K is large (measured per
         # shape in strict order: 8192 x 28672 31.9 -> 28.2 us, but 8192 x 8192 11.0 -> 12.5 us)
         self.prepared_linear = [self.mode == "prepared" or (self.mode == "mixed" and k > 8192)
                                 for _n, _r, k in shape.linears]
+        # several ranks: does linear j's vector get its own finish kernel (words -> plain vector)?
+        # Only where the consumer (the next linear) stages x itself from a plain vector.
+        self.finish_after = [self.world > 1 and self.mode in ("fused", "mixed") and not self.prepared_linear[(j + 1) % 4]
+                             for j in range(4)]
         k_max = max(k for _n, _r, k in shape.linears)
         img_bytes = int(_ffi.lib().axc_cuda_q4k_prepared_x_bytes(k_max // 256))
         self.images = [torch.zeros(img_bytes, dtype=torch.uint8, device=self.device) for _ in range(2)]
@@ -164,10 +168,9 @@ class DecodeSweep:
             self.launches_per_token = 8 * shape.layers + (3 if self.world > 1 else 1)
         elif self.world == 1:
             self.launches_per_token = (4 + sum(self.prepared_linear)) * shape.layers + 1
-        elif self.consumer_polls:
-            self.launches_per_token = 4 * shape.layers + 3
         else:
-            self.launches_per_token = 8 * shape.layers + 2
+            self.launches_per_token = (4 + sum(self.prepared_linear) + sum(self.finish_after)) * shape.layers + 2 \
+                + (0 if all(self.finish_after) else 1)
 
     # -- helpers ---------------------------------------------------------------------------
     def _stream(self) -> int:
@@ -185,7 +188,7 @@ class DecodeSweep:
                                self.rank * rows_local)
             rc = _ffi.lib().axc_cuda_q4k_matvec_fused(w.data_ptr(), C.byref(xsrc), None, rows_local, k // 256,
                                                       C.byref(g), self._stream(), st, tn)
-            if rc == 0 and self.mode == "fused":
+            if rc == 0 and self.finish_after[j]:
                 rc = _ffi.lib().axc_cuda_gather_finish(
                     self.pairs.data_ptr() + off * 8, self.epoch.data_ptr(), self.vec.data_ptr() + off * 4, rows,
                     self._stream(), st, _ffi.AXC_FINISH_OVERLAP_PREVIOUS)
@@ -212,6 +215,10 @@ class DecodeSweep:
                                self.rank * rows_local)
             rc = L.axc_cuda_q4k_matvec_prepared(w.data_ptr(), img, 1 if rms else 0, None, rows_local, k // 256,
                                                 C.byref(g), self._stream(), st, tn)
+            if rc == 0 and self.finish_after[j]:
+                rc = L.axc_cuda_gather_finish(self.pairs.data_ptr() + off * 8, self.epoch.data_ptr(),
+                                              self.vec.data_ptr() + off * 4, rows, self._stream(), st,
+                                              _ffi.AXC_FINISH_OVERLAP_PREVIOUS)
         else:
             rc = L.axc_cuda_q4k_matvec_prepared(w.data_ptr(), img, 1 if rms else 0,
                                                 self.vec.data_ptr() + off * 4, rows_local, k // 256, None,
@@ -219,9 +226,10 @@ class DecodeSweep:
         _raise_for(rc)
 
     def _src(self, layer: int, j: int, word: int = 0, second: Optional[int] = None, rms: bool = True):
-        """x source = output of linear j of `layer` starting at `word` (+ the vector at `second`)."""
+        """x source = output of linear j of `layer` starting at `word` (+ the vector at `second`):
+        the plain vector where a finish kernel unpacked it, else the (value, epoch) words."""
         base = self.offsets[layer][j] + word
-        if self.world > 1 and self.mode != "fused":
+        if self.world > 1 and not self.finish_after[j]:
             p = self.pairs.data_ptr()
             return _ffi.AxcXSrc(None, None, p + base * 8,
                                 None if second is None else p + (self.offsets[layer][j] + second) * 8,
@@ -256,8 +264,8 @@ class DecodeSweep:
                     else:
                         self._linear(layer, j, src)
             last = self.offsets[sh.layers - 1][3]
-            if self.world > 1 and self.mode != "fused":
-                # nothing unpacked the words yet: every vector (k and v included) in one pass
+            if self.world > 1 and not all(self.finish_after):
+                # some vectors were never unpacked: every vector (k and v included) in one pass
                 _raise_for(_ffi.lib().axc_cuda_gather_finish(
                     self.pairs.data_ptr(), self.epoch.data_ptr(), self.vec.data_ptr(),
                     sh.vector_words_per_layer * sh.layers, self._stream(), self.status.data_ptr(), 0))
