@@ -23,8 +23,8 @@ next linear's input is the ``mode``:
   with more than one GPU a finish kernel first unpacks the words into a plain vector.
 * ``"mixed"`` (default on one GPU): "prepared" for the linears with K > 8192 (the down projection),
   "fused" for the others: the faster choice per shape on one GPU.  On several GPUs it runs (the
-  prepare kernel then polls the words of gate+up) but measured slower than "fused" (6.29 against
-  5.72 ms/token on two GPUs).
+  prepare kernel then reads the words of gate+up) but measured slower than "fused" (5.92 against
+  5.73 ms/token on two GPUs).
 * ``"poll"``: as "fused", but every consumer CTA polls the (value, epoch) words itself (no launch in
   between, 2 x the bytes per CTA past L1: measured slower).
 
@@ -247,7 +247,9 @@ class DecodeSweep:
         with torch.cuda.device(self.device):
             if self.world > 1:
                 _raise_for(_ffi.lib().axc_cuda_gather_next_epoch(self.epoch.data_ptr(), self._stream()))
-            ov = self.world > 1      # epoch-word sources: the prepare kernel may start behind its producer
+            # The prepare kernel waits for the launch before it even when its sources are epoch words (it
+            # could start behind its producer and poll, but that measured 3 us slower per linear).
+            ov = False
             for layer in range(sh.layers):
                 if layer == 0:
                     x = _ffi.AxcXSrc(self.h.data_ptr(), None, None, None, None, 1 if normalise_input else 0)
