@@ -569,3 +569,35 @@ def grid_search_tool(req: GridSearchRequest, ctx: McpContext) -> GridSearchRespo
                             "correctness": rv.correctness.to_json_obj()} for rv in ranked],
                 "machine": asdict(out.machine)}})
     return out
+
+
+# ------------------------------------------------------------------ axc optimize
+
+def strategy_sidecar_path(output: str) -> str:
+    """crates/axc-driver/src/optimize.rs:114-125: ``out.spv`` -> ``out.spv.axc.strategy.json``."""
+    return str(output) + ".axc.strategy.json"
+
+
+def run_optimize(req: GridSearchRequest, output: str, ctx: McpContext) -> GridSearchResponse:
+    """The ``axc optimize`` flow (crates/axc-driver/src/optimize.rs:41-112) with a real bench
+    function in place of the reference's fixed 1000 ns mock: grid-search the kernel's launch
+    tunables on the device, then write the winner where the reference writes the winning SPIR-V --
+    here the tuned kernel's metadata sidecar, since the kernel itself is compiled ahead of time --
+    and the search result as ``<output>.axc.strategy.json``."""
+    meta = _resolve_metadata(req)
+    resp = grid_search_tool(req, ctx)
+    meta.save(output)
+    record = {
+        "winner_variant_id": resp.winner_variant_id,
+        "winner_assignments": {"values": resp.winner_assignments},
+        "winner_median_ns": resp.winner_median_ns,
+        "fallback_used": resp.fallback_used,
+        "warnings": resp.warnings,
+        "results": [{"ordinal": rv.ordinal, "variant_id": rv.variant_id, "assignments": {"values": rv.assignments},
+                     "median_ns": rv.median_ns, "device_median_ns": rv.device_median_ns, "outcome": rv.outcome,
+                     "correctness": rv.correctness.to_json_obj()} for rv in sorted(resp.ranked, key=lambda v: v.ordinal)],
+        "machine": asdict(resp.machine),
+    }
+    with open(strategy_sidecar_path(output), "w", encoding="utf-8") as f:
+        json.dump(record, f, indent=2, sort_keys=True)
+    return resp

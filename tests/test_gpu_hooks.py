@@ -107,3 +107,18 @@ def test_grid_search_tool_ranks_tunable_variants(mcp, tmp_path):
     rec = [json.loads(l) for l in open(resp.history_path)]
     assert len(rec) == 1 and rec[0]["grid_search"]["winner_variant_id"] == resp.winner_variant_id
     assert rec[0]["grid_search"]["ranked"][0]["correctness"] == {"status": "ok"}
+
+
+def test_run_optimize_writes_winner_metadata_and_strategy_sidecar(mcp, tmp_path):
+    rows, n = 1024, 16
+    sizes = [rows * n * 144, n * 256 * 4, rows * 4]
+    out = tmp_path / "q4km.tuned.json"
+    req = hooks.GridSearchRequest(sizes, 3, {"stages": [2, 3]}, metadata=hooks.q4_metadata("q4km_dequant_matvec"),
+                                  correctness="fp-tol:4", push_constants_base64=b64(n))
+    resp = hooks.run_optimize(req, str(out), mcp)
+    runtime = load_pkg("runtime")
+    assert runtime.load_kernel_metadata(out).kernel_name == "q4km_dequant_matvec"
+    side = json.loads(open(hooks.strategy_sidecar_path(str(out))).read())
+    assert hooks.strategy_sidecar_path("out.spv") == "out.spv.axc.strategy.json"
+    assert side["winner_assignments"]["values"] == resp.winner_assignments and len(side["results"]) == 2
+    assert [r["ordinal"] for r in side["results"]] == [0, 1] and side["fallback_used"] is False
