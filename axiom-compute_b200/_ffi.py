@@ -63,12 +63,18 @@ class AxcTuning(C.Structure):
 
 class AxcGather(C.Structure):
     _fields_ = [("y_peer_bases", C.c_void_p), ("y_offset_bytes", C.c_uint64), ("epoch", C.c_void_p),
-                ("world", C.c_uint32), ("rank", C.c_uint32), ("row_offset", C.c_uint32)]
+                ("world", C.c_uint32), ("rank", C.c_uint32), ("row_offset", C.c_uint32),
+                ("parity_stride_bytes", C.c_uint64)]
+
+
+class AxcGatherSync(C.Structure):
+    _fields_ = [("done_peer_bases", C.c_void_p), ("done_local", C.c_void_p), ("arrive_counter", C.c_void_p),
+                ("epoch", C.c_void_p), ("world", C.c_uint32), ("rank", C.c_uint32)]
 
 
 class AxcXSrc(C.Structure):
     _fields_ = [("x", C.c_void_p), ("x2", C.c_void_p), ("x_pairs", C.c_void_p), ("x2_pairs", C.c_void_p),
-                ("epoch", C.c_void_p), ("unit_rms", C.c_uint32)]
+                ("epoch", C.c_void_p), ("unit_rms", C.c_uint32), ("parity_stride_bytes", C.c_uint64)]
 
 
 # Every symbol include/axc_cuda.h declares: name -> (restype, argtypes)
@@ -128,8 +134,10 @@ SYMBOLS = {
     "axc_cuda_q4k_matvec_prepared": (C.c_int, [_VP, _VP, C.c_uint32, _VP, C.c_uint32, C.c_uint32,
                                                C.POINTER(AxcGather), _VP, _VP, C.POINTER(AxcTuning)]),
     "axc_cuda_gather_next_epoch": (C.c_int, [_VP, _VP]),
-    "axc_cuda_gather_finish": (C.c_int, [_VP, _VP, _VP, C.c_uint32, _VP, _VP, C.c_uint32]),
+    "axc_cuda_gather_finish": (C.c_int, [_VP, _VP, _VP, C.c_uint32, _VP, _VP, C.c_uint32, C.c_uint64,
+                                         C.POINTER(AxcGatherSync)]),
     "axc_cuda_q4k_matvec_static": (C.c_int, [_VP, _VP, _VP, C.c_uint32, C.c_uint32, _VP]),
+    "axc_cuda_q4k_matvec_static_warmup": (C.c_int, []),
     "axc_cuda_version": (C.c_int, []),
 }
 

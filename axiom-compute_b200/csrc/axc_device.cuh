@@ -16,6 +16,7 @@ constexpr int Q4_0_BLK_ELEMS = 32;
 constexpr uint32_t ERR_BULK_WAIT_TIMEOUT = 1u;  // an mbarrier wait gave up
 constexpr uint32_t ERR_BAD_ARGUMENT = 2u;
 constexpr uint32_t ERR_PEER_WAIT_TIMEOUT = 4u;  // a peer's all-gather flag never arrived
+constexpr uint32_t ERR_EPOCH_AHEAD = 8u;        // an all-gather word from a later step: storage reused too early
 
 // Spin limit for every mbarrier wait.  try_wait itself blocks for a hardware-defined slice,
 // so this is far beyond any legitimate HBM latency yet ends within a fraction of a second.

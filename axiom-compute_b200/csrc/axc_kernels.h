@@ -12,6 +12,16 @@ struct GatherArgs {
     uint64_t y_offset_bytes;       // this call's vector (8 bytes per global row) inside that storage
     const uint32_t* epoch_ptr;     // this rank's epoch counter
     uint32_t world, rank, row_offset;
+    uint64_t parity_stride_bytes = 0;  // odd epochs use a second copy of the storage this far behind the first
+};
+
+// End-of-step handshake of the fused all-gather (see gather_finish_kernel).
+struct GatherSync {
+    const uint64_t* done_peer_bases;  // device array [world]: address of each rank's uint32 done[world]
+    const uint32_t* done_local;       // this rank's own done[world]
+    uint32_t* arrive_counter;         // device uint32, zero before first use
+    uint32_t* epoch_rw;               // the epoch counter (advanced by the finish kernel)
+    uint32_t world, rank;
 };
 
 // Where the streaming matvec takes its activations from when they are not one plain vector:
@@ -25,6 +35,16 @@ struct XSource {
     const uint64_t* x2_pairs = nullptr;
     const uint32_t* epoch_ptr = nullptr;
     int unit_rms = 0;
+    uint64_t parity_stride_bytes = 0;  // (value, epoch) sources: second copy for odd epochs
+};
+
+// Completion signal of the streaming matvec for a host that polls a word in mapped host memory
+// instead of waiting on an event: the last CTA to finish writes `seq` to `flag` after every
+// store of y is visible to the host.  `counter` is one device word, zero before first use.
+struct DoneSignal {
+    uint32_t* counter;
+    uint32_t* flag;
+    uint32_t seq;
 };
 
 // Tunables of the streaming matvec kernels.  0 = let the launcher choose.
@@ -41,7 +61,13 @@ struct MatvecTuning {
     int x_prepared_rms = 0;            // with x_prepared: scale y by 1 / sqrt(mean(x^2))
     const GatherArgs* gather = nullptr;  // all-gather fused into the epilogue (y is ignored)
     const XSource* xsrc = nullptr;       // fused activation source (Q4_K_M only; x is ignored)
+    const DoneSignal* done = nullptr;    // completion signal for a polling host (streaming kernels only)
 };
+
+// True when launch_q4k_matvec / launch_q4_0_matvec take the streaming kernel for this row length
+// (the kernel that supports x_prepared, gather, xsrc and done).
+inline bool q4k_uses_stream_kernel(uint32_t n_sb) { return n_sb >= 1 && n_sb <= 128; }
+inline bool q4_0_uses_stream_kernel(uint32_t n_blocks) { return n_blocks >= 2 && !(n_blocks & 1u) && n_blocks <= 1024u; }
 
 struct LaunchInfo {
     int grid = 0, block = 0;
@@ -69,12 +95,14 @@ cudaError_t launch_q4k_prefill(const uint8_t* q, const uint16_t* a_bf16, float* 
                                bool independent = false /* inputs / C untouched by the launch before */);
 
 cudaError_t launch_gather_finish(const uint64_t* pairs, const uint32_t* epoch_ptr, float* out, uint32_t n,
-                                 uint32_t* status, cudaStream_t stream, bool overlap);
+                                 uint32_t* status, cudaStream_t stream, bool overlap, uint64_t parity_stride = 0,
+                                 const GatherSync* sync = nullptr);
 cudaError_t launch_gather_next_epoch(uint32_t* epoch_ptr, cudaStream_t stream);
 
 // Quantised form of x for `n_pos` 64-column positions (see q4_stream.cu): bytes needed and the
 // kernel that fills them; a matvec launched with tuning.x_prepared set reads it instead of x.
 size_t q4_prepared_x_bytes(uint32_t n_pos);
+cudaError_t preload_q4k_prepared_path();   // load those kernels on the current device, launch nothing
 cudaError_t launch_q4_quantize_x(const float* x, void* out, uint32_t n_pos, cudaStream_t stream);
 // The same from a fused source, one CTA per 64 positions, with the per-group sums of x^2 behind
 // the image (for the unit-RMS scale) and optionally x written out as a plain vector.

@@ -64,6 +64,8 @@ struct Slot {
     uint64_t size = 0;        // allocated bytes (power of two)
     uint64_t valid = 0;       // bytes of the most recent upload
     bool mapped = false;      // dev is the device view of the pinned host buffer (no copies)
+    void* staging_dev = nullptr;  // device view of `staging` when it was allocated mapped (small inputs)
+    bool dev_stale = false;   // staging holds a newer upload than dev (the copy was skipped)
 };
 
 // Output bindings up to this size live in mapped pinned host memory: the kernel's stores go
@@ -71,6 +73,10 @@ struct Slot {
 // several microseconds of latency for a few tens of KB) disappears.  Larger outputs keep a
 // device buffer and one bulk copy.
 constexpr uint64_t kMappedOutputMax = 1u << 20;
+// Activation vectors up to this size keep their staging buffer mapped as well: on the fast path a
+// small kernel reads x from it over PCIe and quantises it once for every CTA of the matvec, so no
+// copy-engine transfer (and no hand-over between the copy and compute engines) precedes the launch.
+constexpr uint64_t kMappedInputMax = 1u << 18;
 
 struct CacheKey {
     uint64_t spirv_hash, plan_hash;
@@ -102,7 +108,10 @@ struct axc_kernel {
     std::mutex mu;  // serialises dispatches on this handle (context.rs:494-519)
     std::vector<Slot> slots;
     uint32_t* status_dev = nullptr;
-    uint32_t* status_host = nullptr;  // pinned
+    uint32_t* status_host = nullptr;  // pinned, mapped: [0] kernel error bits, [4] completion sequence number
+    void* fast_scratch = nullptr;     // device: quantised x image, then the CTA counter of the completion signal
+    size_t fast_image_bytes = 0;
+    uint32_t fast_seq = 0;
     cudaEvent_t ev[5] = {nullptr, nullptr, nullptr, nullptr, nullptr};
 };
 
@@ -139,6 +148,7 @@ void destroy_kernel(axc_kernel* k) {
     DeviceGuard g(k->device);
     for (auto& s : k->slots) free_slot(s);
     if (k->status_host) cudaFreeHost(k->status_host);   // status_dev is its device view
+    if (k->fast_scratch) cudaFree(k->fast_scratch);
     for (auto& e : k->ev)
         if (e) cudaEventDestroy(e);
     delete k;
@@ -178,7 +188,8 @@ bool wait_event(cudaEvent_t ev, uint64_t timeout_ms, cudaError_t* err) {
     }
 }
 
-int ensure_slots(axc_kernel* k, const size_t* input_lens, const size_t* output_sizes, const bool* writable) {
+int ensure_slots(axc_kernel* k, const size_t* input_lens, const size_t* output_sizes, const bool* writable,
+                 int mapped_input = -1) {
     if (k->slots.size() < k->n_bufs) k->slots.resize(k->n_bufs);
     for (uint32_t i = 0; i < k->n_bufs; ++i) {
         const uint64_t need = std::max<uint64_t>(std::max<uint64_t>(input_lens[i], output_sizes[i]), 4);
@@ -208,7 +219,12 @@ int ensure_slots(axc_kernel* k, const size_t* input_lens, const size_t* output_s
             cudaGetLastError();
             return fail(AXC_ERR_BUFFER_ALLOCATION_FAILED, "buffer #%u allocation failed (%llu bytes): cudaMalloc: %s", i, (unsigned long long)need, cudaGetErrorString(e));
         }
-        e = cudaHostAlloc(&s.staging, new_size, cudaHostAllocDefault);
+        const bool map_in = (int)i == mapped_input && new_size <= kMappedInputMax;
+        e = cudaHostAlloc(&s.staging, new_size, map_in ? cudaHostAllocMapped : cudaHostAllocDefault);
+        if (e == cudaSuccess && map_in && cudaHostGetDevicePointer(&s.staging_dev, s.staging, 0) != cudaSuccess) {
+            s.staging_dev = nullptr;   // not fatal: the copy path still works
+            cudaGetLastError();
+        }
         if (e != cudaSuccess) {
             cudaFree(s.dev);
             s = Slot{};
@@ -266,32 +282,58 @@ int classify_kernel(const char* entry_point, const axc_buf_desc* bufs, uint32_t 
     return AXC_OK;
 }
 
+// Bounded wait for the completion word the matvec's last CTA writes to mapped host memory.
+// Cheaper than an event (no extra command behind the kernel, no driver call per poll).  The
+// stream is queried now and then so that a failed launch surfaces as an error, not a timeout.
+bool wait_flag(const volatile uint32_t* flag, uint32_t seq, uint64_t timeout_ms, cudaStream_t st, cudaError_t* err) {
+    using clock = std::chrono::steady_clock;
+    const auto t0 = clock::now();
+    const auto limit = std::chrono::milliseconds(timeout_ms);
+    for (uint32_t spins = 1;; ++spins) {
+        if (*flag == seq) return true;
+#if defined(__x86_64__) || defined(__i386__)
+        __builtin_ia32_pause();
+#endif
+        if ((spins & 1023u) == 0) {
+            const cudaError_t q = cudaStreamQuery(st);
+            if (q == cudaSuccess) {           // everything queued has finished
+                if (*flag == seq) return true;
+                *err = cudaErrorUnknown;      // the kernel ended without signalling
+                return false;
+            }
+            if (q != cudaErrorNotReady) {
+                *err = q;
+                return false;
+            }
+            const auto el = clock::now() - t0;
+            if (el > limit) {
+                *err = cudaErrorNotReady;
+                return false;
+            }
+            if (el > std::chrono::milliseconds(2)) std::this_thread::sleep_for(std::chrono::microseconds(50));
+        }
+    }
+}
+
 int dispatch_locked(axc_ctx* ctx, axc_kernel* k, const uint32_t wg[3], const void* const* inputs,
                     const size_t* input_lens, void* const* outputs, const size_t* output_sizes,
                     const void* pc, axc_dispatch_stats* stats) {
     DeviceGuard g(k->device);
     const bool writable[3] = {false, false, true};   // both kernels: [q, x] read-only, y written
-    int rc = ensure_slots(k, input_lens, output_sizes, k->n_bufs == 3 ? writable : nullptr);
+    int rc = ensure_slots(k, input_lens, output_sizes, k->n_bufs == 3 ? writable : nullptr, k->n_bufs == 3 ? 1 : -1);
     if (rc != AXC_OK) return rc;
     cudaStream_t st = ctx->stream;
     const bool timed = stats != nullptr;
     cudaError_t e;
 
-    if (timed) cudaEventRecord(k->ev[0], st);
+    // ---- host side of the uploads: into the pinned staging buffers ----
     for (uint32_t i = 0; i < k->n_bufs; ++i) {
         if (input_lens[i] == 0) continue;  // resident: keep device contents
         Slot& s = k->slots[i];
         std::memcpy(s.staging, inputs[i], input_lens[i]);
         s.valid = input_lens[i];
-        if (s.mapped) continue;   // the device reads the pinned buffer itself
-        e = cudaMemcpyAsync(s.dev, s.staging, input_lens[i], cudaMemcpyHostToDevice, st);
-        if (e != cudaSuccess) {
-            g_fields.binding = i, g_fields.direction = AXC_COPY_HOST_TO_DEVICE;
-            return fail(AXC_ERR_STAGING_COPY_FAILED, "staging copy failed for binding #%u (HostToDevice): %s", i, cudaGetErrorString(e));
-        }
-        s.valid = input_lens[i];
+        if (!s.mapped) s.dev_stale = true;
     }
-    if (timed) cudaEventRecord(k->ev[1], st);
 
     // ---- geometry: rows from the grid, blocks per row from the push constant ----
     uint32_t n = 0;
@@ -300,7 +342,7 @@ int dispatch_locked(axc_ctx* ctx, axc_kernel* k, const uint32_t wg[3], const voi
     const uint32_t blk_bytes = k->kind == KernelKind::Q4K ? 144u : 18u;
     const uint32_t blk_elems = k->kind == KernelKind::Q4K ? 256u : 32u;
     const Slot& sq = k->slots[0];
-    const Slot& sx = k->slots[1];
+    Slot& sx = k->slots[1];
     Slot& sy = k->slots[2];
     const uint64_t q_have = sq.valid ? sq.valid : sq.size;
     const uint64_t x_have = sx.valid ? sx.valid : sx.size;
@@ -321,6 +363,44 @@ int dispatch_locked(axc_ctx* ctx, axc_kernel* k, const uint32_t wg[3], const voi
         }
     }
 
+    // ---- the fast path: no copy-engine transfer for x, no event ----
+    // x stays in its mapped staging buffer; one small kernel reads it over PCIe and quantises it
+    // once for all CTAs, the matvec (launched behind it with programmatic dependent launch, its
+    // weight stream already running) stores y straight into mapped host memory and its last CTA
+    // publishes a sequence number there, which this thread polls.  Taken whenever the streaming
+    // kernel serves the shape and no device timing was asked for.
+    const uint32_t n_pos = k->kind == KernelKind::Q4K ? n * 4u : n / 2u;
+    bool fast = !timed && rows > 0 && n > 0 && !k->strict.load() && sx.staging_dev && sy.mapped &&
+                !k->tune.x_prepared &&
+                (k->kind == KernelKind::Q4K ? axc::q4k_uses_stream_kernel(n) : axc::q4_0_uses_stream_kernel(n));
+    if (fast && !k->fast_scratch) {
+        const size_t image = (axc::q4_prepared_x_bytes(512) + 255) & ~(size_t)255;   // rows of up to 32768 columns
+        if (cudaMalloc(&k->fast_scratch, image + 256) == cudaSuccess &&
+            cudaMemsetAsync((char*)k->fast_scratch + image, 0, 256, st) == cudaSuccess) {
+            k->fast_image_bytes = image;
+        } else {
+            if (k->fast_scratch) cudaFree(k->fast_scratch);
+            k->fast_scratch = nullptr;
+            cudaGetLastError();
+            fast = false;   // the copy path needs no scratch
+        }
+    }
+
+    if (timed) cudaEventRecord(k->ev[0], st);
+    for (uint32_t i = 0; i < k->n_bufs; ++i) {
+        Slot& s = k->slots[i];
+        if (s.mapped || !s.dev_stale) continue;      // the device reads the pinned buffer itself / nothing new
+        if (fast && i == 1) continue;                // x is consumed from its mapped staging buffer
+        e = cudaMemcpyAsync(s.dev, s.staging, s.valid, cudaMemcpyHostToDevice, st);
+        if (e != cudaSuccess) {
+            g_fields.binding = i, g_fields.direction = AXC_COPY_HOST_TO_DEVICE;
+            return fail(AXC_ERR_STAGING_COPY_FAILED, "staging copy failed for binding #%u (HostToDevice): %s", i, cudaGetErrorString(e));
+        }
+        s.dev_stale = false;
+    }
+    if (timed) cudaEventRecord(k->ev[1], st);
+
+    uint32_t seq = 0;
     if (rows > 0) {
         if (n == 0) {
             e = cudaMemsetAsync(sy.dev, 0, rows * 4, st);  // empty sum: +0.0 per row
@@ -328,41 +408,67 @@ int dispatch_locked(axc_ctx* ctx, axc_kernel* k, const uint32_t wg[3], const voi
             e = k->kind == KernelKind::Q4K
                     ? axc::launch_q4k_matvec_seq((const uint8_t*)sq.dev, (const float*)sx.dev, (float*)sy.dev, (uint32_t)rows, n, st)
                     : axc::launch_q4_0_matvec_seq((const uint8_t*)sq.dev, (const float*)sx.dev, (float*)sy.dev, (uint32_t)rows, n, st);
+        } else if (fast) {
+            axc::XSource src;
+            src.x = (const float*)sx.staging_dev;
+            e = axc::launch_q4_prepare_x(src, k->fast_scratch, nullptr, n_pos, k->status_dev, st, false);
+            if (e == cudaSuccess) {
+                seq = ++k->fast_seq;
+                if (seq == 0) seq = ++k->fast_seq;   // 0 is what a fresh flag word holds
+                axc::DoneSignal done{reinterpret_cast<uint32_t*>((char*)k->fast_scratch + k->fast_image_bytes), k->status_dev + 4, seq};
+                axc::MatvecTuning tune = k->tune;
+                tune.x_prepared = k->fast_scratch;
+                tune.done = &done;
+                e = k->kind == KernelKind::Q4K
+                        ? axc::launch_q4k_matvec((const uint8_t*)sq.dev, nullptr, (float*)sy.dev, (uint32_t)rows, n, k->status_dev, st, tune, k->sm_count, nullptr)
+                        : axc::launch_q4_0_matvec((const uint8_t*)sq.dev, nullptr, (float*)sy.dev, (uint32_t)rows, n, k->status_dev, st, tune, k->sm_count, nullptr);
+            }
         } else {
             const axc::MatvecTuning& tune = k->tune;
             e = k->kind == KernelKind::Q4K
                     ? axc::launch_q4k_matvec((const uint8_t*)sq.dev, (const float*)sx.dev, (float*)sy.dev, (uint32_t)rows, n, k->status_dev, st, tune, k->sm_count, nullptr)
                     : axc::launch_q4_0_matvec((const uint8_t*)sq.dev, (const float*)sx.dev, (float*)sy.dev, (uint32_t)rows, n, k->status_dev, st, tune, k->sm_count, nullptr);
         }
-        if (e != cudaSuccess)
+        if (e != cudaSuccess) {
+            cudaGetLastError();
             return fail(AXC_ERR_QUEUE_SUBMIT_FAILED, "queue submit failed: kernel launch: %s", cudaGetErrorString(e));
+        }
     }
     if (timed) cudaEventRecord(k->ev[2], st);
 
+    bool copies_back = false;
     for (uint32_t i = 0; i < k->n_bufs; ++i) {
         if (output_sizes[i] == 0) continue;
         Slot& s = k->slots[i];
-        if (s.mapped) continue;   // already in host memory when the event completes
+        if (s.mapped) continue;   // already in host memory when the kernel completes
         e = cudaMemcpyAsync(s.staging, s.dev, output_sizes[i], cudaMemcpyDeviceToHost, st);
         if (e != cudaSuccess) {
             g_fields.binding = i, g_fields.direction = AXC_COPY_DEVICE_TO_HOST;
             return fail(AXC_ERR_STAGING_COPY_FAILED, "staging copy failed for binding #%u (DeviceToHost): %s", i, cudaGetErrorString(e));
         }
+        copies_back = true;
     }
-    e = cudaEventRecord(timed ? k->ev[3] : k->ev[4], st);
-    if (e != cudaSuccess)
-        return fail(AXC_ERR_QUEUE_SUBMIT_FAILED, "queue submit failed: %s", cudaGetErrorString(e));
 
     const uint64_t timeout_ms = fence_timeout_ms_for(ctx);
     cudaError_t werr = cudaSuccess;
-    if (!wait_event(timed ? k->ev[3] : k->ev[4], timeout_ms, &werr)) {
+    bool ok;
+    if (seq != 0 && !copies_back) {
+        ok = wait_flag(k->status_host + 4, seq, timeout_ms, st, &werr);
+    } else {
+        e = cudaEventRecord(timed ? k->ev[3] : k->ev[4], st);
+        if (e != cudaSuccess)
+            return fail(AXC_ERR_QUEUE_SUBMIT_FAILED, "queue submit failed: %s", cudaGetErrorString(e));
+        ok = wait_event(timed ? k->ev[3] : k->ev[4], timeout_ms, &werr);
+    }
+    if (!ok) {
         if (werr == cudaErrorNotReady) {
             g_fields.timeout_ns = timeout_ms * 1000000ull;
             return fail(AXC_ERR_FENCE_TIMEOUT, "fence wait timed out after %llu ns", (unsigned long long)g_fields.timeout_ns);
         }
+        cudaGetLastError();
         return fail(AXC_ERR_QUEUE_SUBMIT_FAILED, "queue submit failed: %s", cudaGetErrorString(werr));
     }
-    if (*k->status_host != 0) {
+    if (*(volatile uint32_t*)k->status_host != 0) {
         const uint32_t bits = *k->status_host;
         *k->status_host = 0;
         g_fields.timeout_ns = 0;
@@ -574,7 +680,7 @@ int axc_cuda_prepare_kernel(axc_ctx* ctx, const char* entry_point, const axc_buf
     // bounded wait gives up, and reading it back costs no copy after the kernel.
     cudaError_t e = cudaHostAlloc((void**)&k->status_host, 64, cudaHostAllocMapped);
     if (e == cudaSuccess) {
-        *k->status_host = 0;
+        std::memset(k->status_host, 0, 64);
         e = cudaHostGetDevicePointer((void**)&k->status_dev, k->status_host, 0);
     }
     for (auto& ev : k->ev)
@@ -794,7 +900,7 @@ int axc_cuda_q4k_matvec_allgather(const void* q, const float* x, uint32_t rows_l
                                   uint32_t* status, const axc_tuning* tuning) {
     clear_error();
     if (rows_local == 0) return AXC_OK;
-    if (!g || !g->y_peer_bases || !g->epoch || g->world == 0 || g->world > 16 || g->rank >= g->world || (g->y_offset_bytes & 7u))
+    if (!g || !g->y_peer_bases || !g->epoch || g->world == 0 || g->world > 16 || g->rank >= g->world || ((g->y_offset_bytes | g->parity_stride_bytes) & 7u))
         return fail(AXC_ERR_INVALID_ARGUMENT, "incomplete all-gather description");
     if (!q || !x || (((uintptr_t)q | (uintptr_t)x) & 15u))
         return fail(AXC_ERR_INVALID_ARGUMENT, "q and x must be non-null and 16-byte aligned");
@@ -803,6 +909,7 @@ int axc_cuda_q4k_matvec_allgather(const void* q, const float* x, uint32_t rows_l
     axc::GatherArgs ga{};
     ga.y_peer_bases = g->y_peer_bases, ga.y_offset_bytes = g->y_offset_bytes, ga.epoch_ptr = g->epoch;
     ga.world = g->world, ga.rank = g->rank, ga.row_offset = g->row_offset;
+    ga.parity_stride_bytes = g->parity_stride_bytes;
     axc::MatvecTuning t = to_tuning(tuning);
     t.gather = &ga;
     return launch_result(axc::launch_q4k_matvec((const uint8_t*)q, x, nullptr, rows_local, n_superblocks, status, (cudaStream_t)stream, t, sm_count_of_current_device(), nullptr));
@@ -850,15 +957,17 @@ int axc_cuda_q4k_matvec_fused(const void* q, const axc_xsrc* xs, float* y, uint3
     axc::GatherArgs ga{};
     axc::MatvecTuning t = to_tuning(tuning);
     if (g) {
-        if (!g->y_peer_bases || !g->epoch || g->world == 0 || g->world > 16 || g->rank >= g->world || (g->y_offset_bytes & 7u))
+        if (!g->y_peer_bases || !g->epoch || g->world == 0 || g->world > 16 || g->rank >= g->world || ((g->y_offset_bytes | g->parity_stride_bytes) & 7u))
             return fail(AXC_ERR_INVALID_ARGUMENT, "incomplete all-gather description");
         ga.y_peer_bases = g->y_peer_bases, ga.y_offset_bytes = g->y_offset_bytes, ga.epoch_ptr = g->epoch;
         ga.world = g->world, ga.rank = g->rank, ga.row_offset = g->row_offset;
+        ga.parity_stride_bytes = g->parity_stride_bytes;
         t.gather = &ga;
     }
     axc::XSource src;
     src.x = xs->x, src.x2 = xs->x2, src.x_pairs = xs->x_pairs, src.x2_pairs = xs->x2_pairs;
     src.epoch_ptr = xs->epoch, src.unit_rms = xs->unit_rms ? 1 : 0;
+    src.parity_stride_bytes = xs->parity_stride_bytes;
     t.xsrc = &src;
     return launch_result(axc::launch_q4k_matvec((const uint8_t*)q, nullptr, y, rows, n_superblocks, status, (cudaStream_t)stream, t, sm_count_of_current_device(), nullptr));
 }
@@ -906,10 +1015,11 @@ int axc_cuda_q4k_matvec_prepared(const void* q, const void* image, uint32_t unit
     axc::GatherArgs ga{};
     axc::MatvecTuning t = to_tuning(tuning);
     if (g) {
-        if (!g->y_peer_bases || !g->epoch || g->world == 0 || g->world > 16 || g->rank >= g->world || (g->y_offset_bytes & 7u))
+        if (!g->y_peer_bases || !g->epoch || g->world == 0 || g->world > 16 || g->rank >= g->world || ((g->y_offset_bytes | g->parity_stride_bytes) & 7u))
             return fail(AXC_ERR_INVALID_ARGUMENT, "incomplete all-gather description");
         ga.y_peer_bases = g->y_peer_bases, ga.y_offset_bytes = g->y_offset_bytes, ga.epoch_ptr = g->epoch;
         ga.world = g->world, ga.rank = g->rank, ga.row_offset = g->row_offset;
+        ga.parity_stride_bytes = g->parity_stride_bytes;
         t.gather = &ga;
     }
     t.x_prepared = image, t.x_prepared_rms = unit_rms ? 1 : 0;
@@ -923,12 +1033,25 @@ int axc_cuda_gather_next_epoch(uint32_t* epoch, void* stream) {
 }
 
 int axc_cuda_gather_finish(const uint64_t* pairs, const uint32_t* epoch, float* out, uint32_t n,
-                           void* stream, uint32_t* status, uint32_t flags) {
+                           void* stream, uint32_t* status, uint32_t flags, uint64_t parity_stride_bytes,
+                           const axc_gather_sync* sync) {
     clear_error();
-    if (n == 0) return AXC_OK;
-    if (!pairs || !epoch || !out || ((uintptr_t)pairs & 7u))
+    if (n == 0 && !sync) return AXC_OK;
+    if (!epoch || (n && (!pairs || !out)) || ((uintptr_t)pairs & 7u) || (parity_stride_bytes & 7u))
         return fail(AXC_ERR_INVALID_ARGUMENT, "null or misaligned pair storage / epoch / output");
-    return launch_result(axc::launch_gather_finish(pairs, epoch, out, n, status, (cudaStream_t)stream, (flags & AXC_FINISH_OVERLAP_PREVIOUS) != 0));
+    axc::GatherSync gs{};
+    if (sync) {
+        if (!sync->done_peer_bases || !sync->done_local || !sync->arrive_counter || !sync->epoch ||
+            sync->world == 0 || sync->world > 16 || sync->rank >= sync->world)
+            return fail(AXC_ERR_INVALID_ARGUMENT, "incomplete end-of-step handshake description");
+        if (flags & AXC_FINISH_OVERLAP_PREVIOUS)
+            return fail(AXC_ERR_INVALID_ARGUMENT, "the end-of-step handshake advances the epoch: it cannot overlap the launch before it");
+        gs.done_peer_bases = sync->done_peer_bases, gs.done_local = sync->done_local;
+        gs.arrive_counter = sync->arrive_counter, gs.epoch_rw = sync->epoch, gs.world = sync->world, gs.rank = sync->rank;
+    }
+    return launch_result(axc::launch_gather_finish(pairs, epoch, out, n, status, (cudaStream_t)stream,
+                                                   (flags & AXC_FINISH_OVERLAP_PREVIOUS) != 0, parity_stride_bytes,
+                                                   sync ? &gs : nullptr));
 }
 
 int axc_cuda_q4k_matvec_plan(uint32_t rows, uint32_t n_superblocks, const axc_tuning* tuning,

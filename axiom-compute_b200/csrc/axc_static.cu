@@ -52,6 +52,17 @@ cudaError_t device_scratch(void** out) {
 
 }  // namespace
 
+extern "C" int axc_cuda_q4k_matvec_static_warmup(void) {
+    void* scratch = nullptr;
+    cudaError_t e = device_scratch(&scratch);   // loads the module that holds the array on this device
+    if (e == cudaSuccess) e = axc::preload_q4k_prepared_path();
+    if (e != cudaSuccess) {
+        cudaGetLastError();
+        return AXC_ERR_DEVICE_CREATION_FAILED;
+    }
+    return AXC_OK;
+}
+
 extern "C" int axc_cuda_q4k_matvec_static(const void* q, const float* x, float* y, uint32_t rows,
                                           uint32_t n_superblocks, void* stream) {
     if (rows == 0) return AXC_OK;

@@ -58,6 +58,7 @@ struct StreamParams {
     const uint64_t* x_pairs;
     const uint64_t* x2_pairs;
     const uint32_t* x_epoch_ptr;
+    uint64_t x_parity_stride;  // words of odd epochs live this many bytes behind those of even epochs
     uint32_t x_unit_rms;
     float* y;
     uint32_t* status;
@@ -85,9 +86,27 @@ struct StreamParams {
     // paired with the current epoch in one 8-byte word, into every rank's full-length vector
     const uint64_t* y_peer_bases;  // device array [world]: base address of each rank's pair storage
     uint64_t y_offset_bytes;       // offset of this call's vector (uint2[global rows]) in that storage
+    uint64_t y_parity_stride;      // odd epochs store this many bytes further on (two alternating copies)
     const uint32_t* epoch_ptr;     // this rank's epoch counter (advanced once per step by the caller)
     uint32_t world, rank, row_offset;
+    // completion signal for a host that polls instead of waiting on an event: every CTA counts
+    // itself in after its stores of y; the last one writes done_seq to done_flag (host memory)
+    uint32_t* done_counter;
+    uint32_t* done_flag;
+    uint32_t done_seq;
 };
+
+// One thread per CTA, after the CTA's stores of y (each storing thread has fenced, then a CTA-wide
+// barrier): count this CTA in; the last CTA of the grid resets the counter for the next launch
+// and publishes the sequence number where the host can see it.
+__device__ __forceinline__ void signal_cta_done(const StreamParams& p) {
+    __threadfence_system();
+    if (atomicAdd(p.done_counter, 1u) == gridDim.x - 1) {
+        *p.done_counter = 0;
+        __threadfence_system();
+        asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(p.done_flag), "r"(p.done_seq) : "memory");
+    }
+}
 
 __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
@@ -114,22 +133,46 @@ __device__ __forceinline__ void dp4a_uu(uint32_t& acc, uint32_t a, uint32_t b) {
     asm("dp4a.u32.u32 %0, %1, %2, %0;" : "+r"(acc) : "r"(a), "r"(b));
 }
 
-constexpr int X_FRAC_BITS = 21;  // |x| < 2^(e+1)  ->  |x * 2^(21-e)| < 2^22: top byte in [-64, 63]
+// Fixed point of the activations.  With 2^e <= M < 2^(e+1), M the largest finite |x| of a 64-column
+// chunk, every x of the chunk becomes X = rn(x * 2^(22-e)) clamped to [-2^23, 2^23 - 1]: a 24-bit
+// two's-complement integer, i.e. three byte digits (top one signed, -128..127).  The integer dot
+// products with the 4-bit weights are exact, so the only error of the scheme is |x - X 2^(e-22)| <=
+// 2^(e-23) <= 2^-23 M per element (one unit more for an element the clamp touches):
+//     |y_fixed - y_exact| <= 2^-23 * sum over chunks c of  M_c * sum_{i in c} |w_i|.
+// Measured against sum_i |w_i x_i| (the norm-wise bar) that is <= 2^-23 R = 1.2e-7 R when the |x| of a
+// chunk lie within a factor R of its maximum: far inside 1e-5 for any realistic spread (R <= 80).  An
+// element below 2^-24 of its chunk's maximum is flushed to zero; the bound then still holds but is
+// no longer small RELATIVE to that element's own term, which matters only if the larger elements of
+// the chunk meet weights that are (nearly) zero: the worst case, one element at M with weight 0
+// beside 63 elements of about 2^-24 M, loses those 63 terms entirely, where an fp32 sum keeps 24
+// bits of each.  The tests measure log-uniform spreads over 2^30 inside every chunk.
+constexpr int X_FRAC_BITS = 22;
 
 // Per-thread constants for the life of the CTA.
 struct LaneCtx {
     uint32_t dg[16][3];  // digit words of columns 4k..4k+3 of the position, k = 0..15
-    float sum_a, sum_b;  // sum of x over columns 0..31 / 32..63 of the position
-    float ps_a, ps_b;    // 2^(e - 21) as two representable factors
+    // Q4_K_M: sum of the FIXED-POINT activations over columns 0..31 / 32..63 of the position, in
+    // x's units (so the min term sees exactly the x the integer dot products see); NaN if any x of
+    // that half is not finite.  Q4_0: 0, or NaN if any x of the block is not finite.
+    float sum_a, sum_b;
+    float ps_a, ps_b;    // 2^(e - 22) as two representable factors
     uint32_t sh0, sh_m, sh2, mask_a, mask_b;  // Q4_K_M scale/min unpack selectors for chunk c
     bool big;
+    // Q4_0: start values of the digit sums, -8 * (sum of the digit over the 16 columns a nibble
+    // half meets) and -128 * ... for the high nibbles (which stay multiplied by 16): the sums then
+    // come out as sum((q_i - 8) X_i), exactly, and a block of all-8 nibbles gives exactly zero.
+    int q40_lo[2][3], q40_hi[2][3];
 };
 
 // Exact integer dot of four nibble words with the digit words of columns [4*k0, 4*k0 + 16):
 // low nibbles against dg[k0 + j], high nibbles (left unshifted: times 16) against dg[k1 + j].
 struct DigitSums {
-    uint32_t l0 = 0, l1 = 0, h0 = 0, h1 = 0;  // unsigned digits 0, 1
+    uint32_t l0 = 0, l1 = 0, h0 = 0, h1 = 0;  // digits 0, 1 (unsigned digits; sums may start negative)
     int l2 = 0, h2 = 0;                       // signed top digit
+    __device__ __forceinline__ void start(const int (&lo)[3], const int (&hi)[3]) {
+        l0 = (uint32_t)lo[0], l1 = (uint32_t)lo[1], l2 = lo[2];
+        h0 = (uint32_t)hi[0], h1 = (uint32_t)hi[1], h2 = hi[2];
+    }
     __device__ __forceinline__ void add(uint32_t w, const uint32_t (&lo)[3], const uint32_t (&hi)[3]) {
         const uint32_t lo4 = w & 0x0F0F0F0Fu, hi4 = w & 0xF0F0F0F0u;
         dp4a_uu(l0, lo4, lo[0]);
@@ -143,6 +186,13 @@ struct DigitSums {
     __device__ __forceinline__ float low() const { return fmaf((float)l2, 65536.0f, (float)(l1 * 256u + l0)); }
     __device__ __forceinline__ float high() const {  // carries the factor 16 of the unshifted nibbles
         return fmaf((float)h2, 4096.0f, (float)(h1 * 256u + h0) * 0.0625f);
+    }
+    // the same when the sums may be negative (Q4_0 start values)
+    __device__ __forceinline__ float low_signed() const {
+        return fmaf((float)l2, 65536.0f, (float)(int)(l1 * 256u + l0));
+    }
+    __device__ __forceinline__ float high_signed() const {
+        return fmaf((float)h2, 4096.0f, (float)(int)(h1 * 256u + h0) * 0.0625f);
     }
 };
 
@@ -184,6 +234,8 @@ __device__ __forceinline__ float q40_pos_dot(const uint8_t* pair_ptr, const Lane
 #pragma unroll
     for (int i = 0; i < 9; ++i) W[i] = wp[i];
     DigitSums s0, s1;
+    s0.start(t.q40_lo[0], t.q40_hi[0]);
+    s1.start(t.q40_lo[1], t.q40_hi[1]);
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
         // block 0: its 16 nibble bytes straddle the words by 16 bits
@@ -192,19 +244,20 @@ __device__ __forceinline__ float q40_pos_dot(const uint8_t* pair_ptr, const Lane
     }
     const float d0 = f16_bits_to_f32(W[0] & 0xFFFFu);
     const float d1 = f16_bits_to_f32(W[4] >> 16);
-    // d * (sum(q_i x_i) - 8 * sum(x_i)) per block
-    const float a0 = ((s0.low() + s0.high()) * t.ps_a) * t.ps_b;
-    const float a1 = ((s1.low() + s1.high()) * t.ps_a) * t.ps_b;
-    return fmaf(d1, fmaf(-8.0f, t.sum_b, a1), d0 * fmaf(-8.0f, t.sum_a, a0));
+    // d * sum((q_i - 8) x_i) per block; sum_a / sum_b are 0, or NaN for a non-finite x
+    const float a0 = ((s0.low_signed() + s0.high_signed()) * t.ps_a) * t.ps_b + t.sum_a;
+    const float a1 = ((s1.low_signed() + s1.high_signed()) * t.ps_a) * t.ps_b + t.sum_b;
+    return fmaf(d1, a1, d0 * a0);
 }
 
-// Four activations scaled by f1 * f2 (= 2^(21-e)) and rounded to integers -> three digit words:
+// Four activations scaled by f1 * f2 (= 2^(22-e)) and rounded to integers -> three digit words:
 // word j holds byte j of the four integers (a 4 x 4 byte transpose).
 __device__ __forceinline__ uint4 quantize_x4(const float4 v, float f1, float f2) {
-    const uint32_t x0 = (uint32_t)__float2int_rn(v.x * f1 * f2);
-    const uint32_t x1 = (uint32_t)__float2int_rn(v.y * f1 * f2);
-    const uint32_t x2 = (uint32_t)__float2int_rn(v.z * f1 * f2);
-    const uint32_t x3 = (uint32_t)__float2int_rn(v.w * f1 * f2);
+    constexpr int kTop = (1 << 23) - 1;   // an |x| just below 2^(e+1) would round up to 2^23
+    const uint32_t x0 = (uint32_t)min(__float2int_rn(v.x * f1 * f2), kTop);
+    const uint32_t x1 = (uint32_t)min(__float2int_rn(v.y * f1 * f2), kTop);
+    const uint32_t x2 = (uint32_t)min(__float2int_rn(v.z * f1 * f2), kTop);
+    const uint32_t x3 = (uint32_t)min(__float2int_rn(v.w * f1 * f2), kTop);
     const uint32_t t01 = __byte_perm(x0, x1, 0x5140);  // x0.b0 x1.b0 x0.b1 x1.b1
     const uint32_t t23 = __byte_perm(x2, x3, 0x5140);
     const uint32_t u01 = __byte_perm(x0, x1, 0x0062);  // x0.b2 x1.b2 . .
@@ -245,8 +298,8 @@ __device__ __forceinline__ float warp_reduce_transposed(const float (&v)[PASSES]
 // a position: thread (pos, qt) loads columns 16qt..16qt+15 (coalesced across the warp), i.e. the
 // four nibble words k = 4qt..4qt+3, so each float4 is one dp4a operand set.  Stored as
 // xs[k][pos] with an XOR swizzle so that these stores and the per-thread reads of the matvec
-// are free of shared-memory bank conflicts; xm[pos] = (sum of columns 0..31, sum of columns
-// 32..63, two factors of 2^(e-21)).  `nthreads` is a multiple of 32; all threads must call.
+// are free of shared-memory bank conflicts; xm[pos] = (0 or NaN: is any x of columns 0..31 not
+// finite, the same for columns 32..63, two factors of 2^(e-22)).  `nthreads` is a multiple of 32; all threads must call.
 // `load16(i, v)` fills v[0..3] with columns 4i..4i+15.  Returns this thread's share of sum(x^2).
 template <class Load16>
 __device__ __forceinline__ float quantize_x_positions_from(Load16 load16, uint4* xs, float4* xm,
@@ -280,7 +333,7 @@ __device__ __forceinline__ float quantize_x_positions_from(Load16 load16, uint4*
             m = fminf(m, __int_as_float(0x7F7FFFFF));  // an infinite x makes the row non-finite anyway
             int e = (int)((__float_as_uint(m) >> 23) & 0xFFu) - 127;
             if (e < -126) e = -126;
-            const int up = X_FRAC_BITS - e;  // [-106, 147]: two representable power-of-two steps
+            const int up = X_FRAC_BITS - e;  // [-105, 148]: two representable power-of-two steps
             const int up1 = up >> 1;
             const float f1 = exp2i(up1), f2 = exp2i(up - up1);
             if (valid) {
@@ -290,8 +343,9 @@ __device__ __forceinline__ float quantize_x_positions_from(Load16 load16, uint4*
                     xs[k * pitch + (pos ^ (k & 7u))] = quantize_x4(v[u], f1, f2);
                 }
                 if (qt == 0) {
-                    const int dn = -up, dn1 = dn >> 1;  // e - 21 in [-147, 106]
-                    xm[pos] = make_float4(s, s_other, exp2i(dn1), exp2i(dn - dn1));
+                    const int dn = -up, dn1 = dn >> 1;  // e - 22 in [-148, 105]
+                    // 0 (finite) or NaN (an infinite or NaN x in that half): what the integers cannot carry
+                    xm[pos] = make_float4(s * 0.0f, s_other * 0.0f, exp2i(dn1), exp2i(dn - dn1));
                 }
             }
         }
@@ -312,34 +366,53 @@ __device__ __forceinline__ void quantize_x_positions(const float* __restrict__ x
 }
 
 // Sixteen columns (4i .. 4i+15) of a (value, epoch) vector.  All eight 16-byte loads are issued
-// together (bypassing L1) and the epochs checked afterwards; only if a word is still old does the
-// thread poll, bounded, until all sixteen carry an epoch >= `epoch`.  After one timeout the
-// thread only looks once at later words.
-__device__ __forceinline__ void load_pairs16(const uint64_t* base, uint32_t i, uint32_t epoch, bool& gave_up,
+// together (bypassing L1) as pairs of 64-bit elements, so value and epoch of a word come from one
+// store, and the epochs are checked afterwards; only if a word is still old does the thread poll,
+// bounded, until all sixteen carry `epoch`.  A word from a LATER epoch means that a producer ran
+// ahead of this reader (the storage was reused too early): that is reported, never accepted.
+// After one timeout the thread only looks once at later words.
+struct PairWait {
+    bool gave_up = false, ahead = false;
+};
+
+__device__ __forceinline__ void load_pairs16(const uint64_t* base, uint32_t i, uint32_t epoch, PairWait& pw,
                                              float4* v) {
-    const uint4* src = reinterpret_cast<const uint4*>(base) + 2 * (size_t)i;
-    uint4 w[8];
-    uint32_t it = gave_up ? (1u << 20) - 1u : 0u;
+    const uint64_t* src = base + 4 * (size_t)i;
+    uint64_t w[16];
+    uint32_t it = pw.gave_up ? (1u << 20) - 1u : 0u;
     for (;;) {
 #pragma unroll
         for (int u = 0; u < 8; ++u)
-            asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];"
-                         : "=r"(w[u].x), "=r"(w[u].y), "=r"(w[u].z), "=r"(w[u].w) : "l"(src + u) : "memory");
-        bool ok = true;
+            asm volatile("ld.relaxed.sys.global.v2.u64 {%0, %1}, [%2];"
+                         : "=l"(w[2 * u]), "=l"(w[2 * u + 1]) : "l"(src + 2 * u) : "memory");
+        bool ok = true, ahead = false;
 #pragma unroll
-        for (int u = 0; u < 8; ++u)
-            ok = ok && (int32_t)(w[u].y - epoch) >= 0 && (int32_t)(w[u].w - epoch) >= 0;
+        for (int u = 0; u < 16; ++u) {
+            const int32_t d = (int32_t)((uint32_t)(w[u] >> 32) - epoch);
+            ok = ok && d == 0;
+            ahead = ahead || d > 0;
+        }
         if (ok) break;
+        if (ahead) {
+            pw.ahead = true;
+            break;
+        }
         if (++it >= (1u << 20)) {
-            gave_up = true;
+            pw.gave_up = true;
             break;
         }
         __nanosleep(64);
     }
 #pragma unroll
     for (int u = 0; u < 4; ++u)
-        v[u] = make_float4(__uint_as_float(w[2 * u].x), __uint_as_float(w[2 * u].z),
-                           __uint_as_float(w[2 * u + 1].x), __uint_as_float(w[2 * u + 1].z));
+        v[u] = make_float4(__uint_as_float((uint32_t)w[4 * u]), __uint_as_float((uint32_t)w[4 * u + 1]),
+                           __uint_as_float((uint32_t)w[4 * u + 2]), __uint_as_float((uint32_t)w[4 * u + 3]));
+}
+
+__device__ __forceinline__ void report_pair_wait(const PairWait& pw, uint32_t* status) {
+    if (!status) return;
+    if (pw.gave_up) atomicOr(status, ERR_PEER_WAIT_TIMEOUT);
+    if (pw.ahead) atomicOr(status, ERR_EPOCH_AHEAD);
 }
 
 template <int FMT, int PASSES, bool PREPARED, bool GATHER, bool XFUSE>
@@ -357,8 +430,10 @@ __global__ void __launch_bounds__(512, 1) q4_matvec_stream_kernel(const StreamPa
     uint4* xs = reinterpret_cast<uint4*>(smem + p.xs_offset);    // [16][x_pitch] digit words
     float4* xm = reinterpret_cast<float4*>(smem + p.xm_offset);  // [x_pitch] sums and scale
 
-    // Let the next grid in the stream be scheduled as early as the hardware allows.
-    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    // A launch declared independent lets the next grid be scheduled at once.  An ordered launch
+    // does so only after its own dependency wait (below): a grid scheduled behind it may read its
+    // inputs without waiting, and must then find every earlier launch of the stream complete.
+    if (p.independent) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
     // Rows owned by this CTA: an even split computed on the host (no CTA has more than one
     // extra row).
@@ -366,7 +441,10 @@ __global__ void __launch_bounds__(512, 1) q4_matvec_stream_kernel(const StreamPa
     const uint32_t r0 = bid * p.rows_base + min(bid, p.rows_rem);
     const uint32_t my_rows = p.rows_base + (bid < p.rows_rem ? 1u : 0u);
     const uint32_t r1 = r0 + my_rows;
-    if (my_rows == 0) return;
+    if (my_rows == 0) {
+        if (p.done_flag && tid == 0) signal_cta_done(p);
+        return;
+    }
     const uint32_t n_tiles = bid < p.rows_rem ? p.tiles_hi : p.tiles_lo;
     const uint32_t row_bytes = p.row_bytes;
 
@@ -419,7 +497,10 @@ __global__ void __launch_bounds__(512, 1) q4_matvec_stream_kernel(const StreamPa
     // x may be the output of the previous kernel in the stream; y may still be read by it.
     // A caller that knows neither is the case (say the up projection launched right after the
     // gate projection of the same x) lets the whole prologue overlap the previous kernel.
-    if (!p.independent) asm volatile("griddepcontrol.wait;" ::: "memory");
+    if (!p.independent) {
+        asm volatile("griddepcontrol.wait;" ::: "memory");
+        asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    }
     // Fused all-gather: the peer addresses never change; the epoch was advanced by an earlier
     // kernel of the stream, so it is read on this side of the wait (through L2, not a cached line).
     __shared__ uint64_t peer_base[16];
@@ -438,21 +519,24 @@ __global__ void __launch_bounds__(512, 1) q4_matvec_stream_kernel(const StreamPa
         uint32_t x_epoch = 0;
         if (p.x_pairs || p.x2_pairs)
             asm volatile("ld.relaxed.gpu.global.u32 %0, [%1];" : "=r"(x_epoch) : "l"(p.x_epoch_ptr) : "memory");
-        bool gave_up = false;
+        PairWait pw;
         const float4* xa = reinterpret_cast<const float4*>(p.x);
         const float4* xb = reinterpret_cast<const float4*>(p.x2);
+        const size_t x_par = (size_t)(x_epoch & 1u) * (p.x_parity_stride >> 3);   // in words
+        const uint64_t* xp1 = p.x_pairs ? p.x_pairs + x_par : nullptr;
+        const uint64_t* xp2 = p.x2_pairs ? p.x2_pairs + x_par : nullptr;
         float sq = quantize_x_positions_from(
             [&](uint32_t i, float4* v) {
-                if (p.x_pairs) {
-                    load_pairs16(p.x_pairs, i, x_epoch, gave_up, v);
+                if (xp1) {
+                    load_pairs16(xp1, i, x_epoch, pw, v);
                 } else {
 #pragma unroll
                     for (int u = 0; u < 4; ++u) v[u] = __ldg(xa + i + u);
                 }
-                if (p.x2_pairs || xb) {
+                if (xp2 || xb) {
                     float4 w[4];
-                    if (p.x2_pairs) {
-                        load_pairs16(p.x2_pairs, i, x_epoch, gave_up, w);
+                    if (xp2) {
+                        load_pairs16(xp2, i, x_epoch, pw, w);
                     } else {
 #pragma unroll
                         for (int u = 0; u < 4; ++u) w[u] = __ldg(xb + i + u);
@@ -463,7 +547,7 @@ __global__ void __launch_bounds__(512, 1) q4_matvec_stream_kernel(const StreamPa
                 }
             },
             xs, xm, p.n_pos, p.x_pos_end, p.x_pitch, tid, blockDim.x);
-        if (gave_up && p.status) atomicOr(p.status, ERR_PEER_WAIT_TIMEOUT);
+        report_pair_wait(pw, p.status);
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) sq += __shfl_xor_sync(0xFFFFFFFFu, sq, o);
         if (lane == 0) sumsq_part[warp] = sq;
@@ -491,7 +575,37 @@ __global__ void __launch_bounds__(512, 1) q4_matvec_stream_kernel(const StreamPa
             ctx.dg[k][0] = a.x, ctx.dg[k][1] = a.y, ctx.dg[k][2] = a.z;
         }
         const float4 meta = xm_src[pos];
-        ctx.sum_a = meta.x, ctx.sum_b = meta.y, ctx.ps_a = meta.z, ctx.ps_b = meta.w;
+        ctx.ps_a = meta.z, ctx.ps_b = meta.w;
+        // sums of each digit over a group of columns: bytes dotted with ones (exact)
+        auto digit_sums = [&](int k0, int nk, int (&out)[3]) {
+            uint32_t s0 = 0, s1 = 0;
+            int s2 = 0;
+#pragma unroll
+            for (int k = k0; k < k0 + nk; ++k) {
+                dp4a_uu(s0, ctx.dg[k][0], 0x01010101u);
+                dp4a_uu(s1, ctx.dg[k][1], 0x01010101u);
+                dp4a_us(s2, 0x01010101u, ctx.dg[k][2]);
+            }
+            out[0] = (int)s0, out[1] = (int)s1, out[2] = s2;
+        };
+        if constexpr (FMT == FMT_Q4K) {
+            int a[3], b[3];
+            digit_sums(0, 8, a);
+            digit_sums(8, 8, b);
+            // |sum of 32 values below 2^23| < 2^28: exact in int32
+            ctx.sum_a = ((float)(a[0] + 256 * a[1] + 65536 * a[2]) * meta.z) * meta.w + meta.x;
+            ctx.sum_b = ((float)(b[0] + 256 * b[1] + 65536 * b[2]) * meta.z) * meta.w + meta.y;
+        } else {
+            ctx.sum_a = meta.x, ctx.sum_b = meta.y;
+#pragma unroll
+            for (int blk = 0; blk < 2; ++blk) {
+                int lo[3], hi[3];
+                digit_sums(8 * blk, 4, lo);
+                digit_sums(8 * blk + 4, 4, hi);
+#pragma unroll
+                for (int d = 0; d < 3; ++d) ctx.q40_lo[blk][d] = -8 * lo[d], ctx.q40_hi[blk][d] = -128 * hi[d];
+            }
+        }
     }
 
     // Lanes past the end of the row read position 0 and are zeroed below.
@@ -593,11 +707,17 @@ __global__ void __launch_bounds__(512, 1) q4_matvec_stream_kernel(const StreamPa
             for (uint32_t wv = 1; wv < wpr; ++wv) sum += part[r * wpr + wv];
             if constexpr (XFUSE || PREPARED) sum *= out_scale;
             const uint64_t word = ((uint64_t)epoch << 32) | (uint64_t)__float_as_uint(sum);
+            const uint64_t par = (uint64_t)(epoch & 1u) * p.y_parity_stride;
             for (uint32_t pr = 0; pr < p.world; ++pr) {
-                uint64_t* dst = reinterpret_cast<uint64_t*>(peer_base[pr]) + (p.row_offset + r0 + r);
+                uint64_t* dst = reinterpret_cast<uint64_t*>(peer_base[pr] + par) + (p.row_offset + r0 + r);
                 asm volatile("st.relaxed.sys.global.b64 [%0], %1;" ::"l"(dst), "l"(word) : "memory");
             }
         }
+    }
+    if (p.done_flag) {
+        __threadfence_system();   // this thread's stores of y, possibly to host memory
+        __syncthreads();
+        if (tid == 0) signal_cta_done(p);
     }
 }
 
@@ -716,18 +836,21 @@ static cudaError_t launch_stream(const uint8_t* q, const float* x, float* y, uin
     p.prefetch_first = tune.pdl >= 2 || tune.pdl < 0 ? 1u : 0u;
     // a prepared x is the output of the launch directly before: never read it ahead of the wait
     p.independent = tune.pdl == 3 && !tune.x_prepared ? 1u : 0u;
+    if (tune.done) p.done_counter = tune.done->counter, p.done_flag = tune.done->flag, p.done_seq = tune.done->seq;
 
     void (*kern)(StreamParams) = nullptr;
     if (tune.gather) {
         const GatherArgs& g = *tune.gather;
         p.y_peer_bases = g.y_peer_bases, p.y_offset_bytes = g.y_offset_bytes, p.epoch_ptr = g.epoch_ptr;
         p.world = g.world, p.rank = g.rank, p.row_offset = g.row_offset;
+        p.y_parity_stride = g.parity_stride_bytes;
     }
     if (tune.xsrc) {
         if (FMT != FMT_Q4K || tune.x_prepared) return cudaErrorInvalidValue;
         const XSource& s = *tune.xsrc;
         p.x = s.x, p.x2 = s.x2, p.x_pairs = s.x_pairs, p.x2_pairs = s.x2_pairs;
         p.x_epoch_ptr = s.epoch_ptr, p.x_unit_rms = s.unit_rms ? 1u : 0u;
+        p.x_parity_stride = s.parity_stride_bytes;
         if constexpr (FMT == FMT_Q4K) {
             if (tune.gather) {
                 switch (passes) {
@@ -790,46 +913,98 @@ static cudaError_t launch_stream(const uint8_t* q, const float* x, float* y, uin
 
 // Consumer side of the fused all-gather: waits until every (value, epoch) word of `pairs` carries
 // the current epoch and writes the values out as a plain fp32 vector.  Bounded (about two seconds
-// per element that never arrives), then ERR_PEER_WAIT_TIMEOUT and the stale value is written.
-// With `overlap` the kernel does not wait for the launch before it (whose words it polls for
-// anyway): the caller guarantees that launch neither advances the epoch nor touches `out`.
+// per element that never arrives), then ERR_PEER_WAIT_TIMEOUT and the stale value is written; a
+// word from a later epoch (a producer ran ahead: the storage was reused too early) sets
+// ERR_EPOCH_AHEAD.  With `overlap` the kernel does not wait for the launch before it (whose words
+// it polls for anyway): the caller guarantees that launch neither advances the epoch nor touches
+// `out`.  With `sync` the last CTA to finish ends the step for this rank: it tells every rank that
+// this rank has consumed epoch e (a peer store into each rank's `done` array), waits (bounded)
+// until every rank has consumed epoch e - 1, i.e. until the copy of the storage that epoch e + 1
+// writes into is free everywhere, and advances the epoch counter.
+struct FinishSync {
+    const uint64_t* done_peer_bases;  // device array [world]: address of each rank's uint32 done[world]
+    const uint32_t* done_local;       // this rank's own done[world]
+    uint32_t* arrive_counter;         // CTAs of this launch that are done; reset by the last one
+    uint32_t* epoch_rw;               // the epoch counter, advanced at the end
+    uint32_t world, rank;
+};
+
 __global__ void gather_finish_kernel(const uint64_t* __restrict__ pairs, const uint32_t* __restrict__ epoch_ptr,
-                                     float* __restrict__ out, uint32_t n, uint32_t* status, uint32_t overlap) {
-    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+                                     float* __restrict__ out, uint32_t n, uint32_t* status, uint32_t overlap,
+                                     uint64_t parity_stride, const FinishSync sync) {
     if (!overlap) asm volatile("griddepcontrol.wait;" ::: "memory");
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");   // ordered: only after the wait
     uint32_t epoch;
     asm volatile("ld.relaxed.gpu.global.u32 %0, [%1];" : "=r"(epoch) : "l"(epoch_ptr) : "memory");
-    bool gave_up = false;
+    pairs += (size_t)(epoch & 1u) * (parity_stride >> 3);
+    bool gave_up = false, ahead = false;
     for (uint32_t i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) {
         uint64_t w = 0;
         uint32_t it = gave_up ? (1u << 22) - 1u : 0u;   // after one timeout the rest get a single look
         for (; it < (1u << 22); ++it) {
             asm volatile("ld.relaxed.sys.global.b64 %0, [%1];" : "=l"(w) : "l"(pairs + i) : "memory");
-            if ((int32_t)((uint32_t)(w >> 32) - epoch) >= 0) break;
+            const int32_t d = (int32_t)((uint32_t)(w >> 32) - epoch);
+            if (d == 0) break;
+            if (d > 0) {
+                ahead = true;
+                break;
+            }
             __nanosleep(100);
         }
-        if (it == (1u << 22)) {
-            gave_up = true;
-            if (status) atomicOr(status, ERR_PEER_WAIT_TIMEOUT);
-        }
+        if (it == (1u << 22)) gave_up = true;
         out[i] = __uint_as_float((uint32_t)w);
     }
+    if (status) {
+        if (gave_up) atomicOr(status, ERR_PEER_WAIT_TIMEOUT);
+        if (ahead) atomicOr(status, ERR_EPOCH_AHEAD);
+    }
+    if (sync.arrive_counter == nullptr) return;
+    __syncthreads();   // every thread of the CTA has read its words
+    if (threadIdx.x != 0) return;
+    __threadfence();
+    if (atomicAdd(sync.arrive_counter, 1u) != gridDim.x - 1) return;
+    *sync.arrive_counter = 0;   // for the next launch (stream order)
+    for (uint32_t r = 0; r < sync.world; ++r) {
+        uint32_t* dst = reinterpret_cast<uint32_t*>(sync.done_peer_bases[r]) + sync.rank;
+        asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(dst), "r"(epoch) : "memory");
+    }
+    bool late = false;
+    for (uint32_t r = 0; r < sync.world; ++r) {
+        uint32_t it = 0;
+        for (; it < (1u << 22); ++it) {
+            uint32_t d;
+            asm volatile("ld.relaxed.sys.global.u32 %0, [%1];" : "=r"(d) : "l"(sync.done_local + r) : "memory");
+            if ((int32_t)(d - (epoch - 1u)) >= 0) break;
+            __nanosleep(100);
+        }
+        late = late || it == (1u << 22);
+    }
+    if (late && status) atomicOr(status, ERR_PEER_WAIT_TIMEOUT);
+    *sync.epoch_rw = epoch + 1u;
 }
 
 __global__ void gather_next_epoch_kernel(uint32_t* epoch_ptr) { *epoch_ptr += 1; }
 
 cudaError_t launch_gather_finish(const uint64_t* pairs, const uint32_t* epoch_ptr, float* out, uint32_t n,
-                                 uint32_t* status, cudaStream_t stream, bool overlap) {
-    if (n == 0) return cudaSuccess;
+                                 uint32_t* status, cudaStream_t stream, bool overlap, uint64_t parity_stride,
+                                 const GatherSync* gs) {
+    if (n == 0 && !gs) return cudaSuccess;
     uint32_t blocks = (n + 255) / 256;
     if (blocks > 592) blocks = 592;
+    if (blocks < 1) blocks = 1;
+    FinishSync fs{};
+    if (gs) {
+        fs.done_peer_bases = gs->done_peer_bases, fs.done_local = gs->done_local;
+        fs.arrive_counter = gs->arrive_counter, fs.epoch_rw = gs->epoch_rw, fs.world = gs->world, fs.rank = gs->rank;
+    }
     cudaLaunchConfig_t cfg{};
     cfg.gridDim = dim3(blocks), cfg.blockDim = dim3(256), cfg.stream = stream;
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr, cfg.numAttrs = 1;
-    return cudaLaunchKernelEx(&cfg, gather_finish_kernel, pairs, epoch_ptr, out, n, status, overlap ? 1u : 0u);
+    return cudaLaunchKernelEx(&cfg, gather_finish_kernel, pairs, epoch_ptr, out, n, status, overlap ? 1u : 0u,
+                              parity_stride, fs);
 }
 
 cudaError_t launch_gather_next_epoch(uint32_t* epoch_ptr, cudaStream_t stream) {
@@ -856,6 +1031,7 @@ struct PrepareParams {
     const uint64_t* x_pairs;
     const uint64_t* x2_pairs;
     const uint32_t* epoch_ptr;
+    uint64_t parity_stride;
     uint4* image;
     float* plain_out;
     uint32_t* status;
@@ -863,16 +1039,19 @@ struct PrepareParams {
 };
 
 __global__ void __launch_bounds__(256) q4_prepare_x_kernel(const PrepareParams p) {
-    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     if (!p.overlap) asm volatile("griddepcontrol.wait;" ::: "memory");
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");   // ordered: only after the wait
     __shared__ float warp_sq[8];
     const uint32_t tid = threadIdx.x, lane = tid & 31u, warp = tid >> 5;
     uint32_t epoch = 0;
     if (p.x_pairs || p.x2_pairs)
         asm volatile("ld.relaxed.gpu.global.u32 %0, [%1];" : "=r"(epoch) : "l"(p.epoch_ptr) : "memory");
-    bool gave_up = false;
+    PairWait pw;
     const float4* xa = reinterpret_cast<const float4*>(p.x);
     const float4* xb = reinterpret_cast<const float4*>(p.x2);
+    const size_t x_par = (size_t)(epoch & 1u) * (p.parity_stride >> 3);
+    const uint64_t* xp1 = p.x_pairs ? p.x_pairs + x_par : nullptr;
+    const uint64_t* xp2 = p.x2_pairs ? p.x2_pairs + x_par : nullptr;
     float4* po = reinterpret_cast<float4*>(p.plain_out);
     // whole warps stay in the loop together (it shuffles): the end is rounded up to 8 positions,
     // positions past n_pos are skipped inside
@@ -880,16 +1059,16 @@ __global__ void __launch_bounds__(256) q4_prepare_x_kernel(const PrepareParams p
     const uint32_t pos1 = min(pos0 + 64u, p.pitch);
     float sq = quantize_x_positions_from(
         [&](uint32_t i, float4* v) {
-            if (p.x_pairs) {
-                load_pairs16(p.x_pairs, i, epoch, gave_up, v);
+            if (xp1) {
+                load_pairs16(xp1, i, epoch, pw, v);
             } else {
 #pragma unroll
                 for (int u = 0; u < 4; ++u) v[u] = __ldg(xa + i + u);
             }
-            if (p.x2_pairs || xb) {
+            if (xp2 || xb) {
                 float4 w[4];
-                if (p.x2_pairs) {
-                    load_pairs16(p.x2_pairs, i, epoch, gave_up, w);
+                if (xp2) {
+                    load_pairs16(xp2, i, epoch, pw, w);
                 } else {
 #pragma unroll
                     for (int u = 0; u < 4; ++u) w[u] = __ldg(xb + i + u);
@@ -903,7 +1082,7 @@ __global__ void __launch_bounds__(256) q4_prepare_x_kernel(const PrepareParams p
             }
         },
         p.image, reinterpret_cast<float4*>(p.image + 16u * p.pitch), p.n_pos, pos1, p.pitch, tid, blockDim.x, pos0);
-    if (gave_up && p.status) atomicOr(p.status, ERR_PEER_WAIT_TIMEOUT);
+    report_pair_wait(pw, p.status);
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) sq += __shfl_xor_sync(0xFFFFFFFFu, sq, o);
     if (lane == 0) warp_sq[warp] = sq;
@@ -913,6 +1092,25 @@ __global__ void __launch_bounds__(256) q4_prepare_x_kernel(const PrepareParams p
         for (uint32_t w = 0; w < 8u; ++w) tot += warp_sq[w];
         reinterpret_cast<float*>(p.image + 17u * p.pitch)[blockIdx.x] = tot;
     }
+}
+
+// Loads (without launching) the kernels of the prepared-x Q4_K_M path on the current device: the
+// stand-alone quantiser and the three tile heights of the matvec.  With lazy module loading the
+// first use of a kernel otherwise loads it at that moment, which may allocate device memory.
+cudaError_t preload_q4k_prepared_path() {
+    cudaFuncAttributes a;
+    cudaError_t e = cudaFuncGetAttributes(&a, q4_quantize_x_kernel);
+    if (e == cudaSuccess) e = cudaFuncGetAttributes(&a, q4_matvec_stream_kernel<FMT_Q4K, 1, true, false, false>);
+    if (e == cudaSuccess) e = cudaFuncGetAttributes(&a, q4_matvec_stream_kernel<FMT_Q4K, 2, true, false, false>);
+    if (e == cudaSuccess) e = cudaFuncGetAttributes(&a, q4_matvec_stream_kernel<FMT_Q4K, 4, true, false, false>);
+    if (e == cudaSuccess) {
+        // the largest dynamic shared-memory request any launch of these kernels makes
+        const size_t smem = (size_t)227 * 1024 - 1024;
+        e = ensure_dynamic_smem(reinterpret_cast<const void*>(q4_matvec_stream_kernel<FMT_Q4K, 1, true, false, false>), smem);
+        if (e == cudaSuccess) e = ensure_dynamic_smem(reinterpret_cast<const void*>(q4_matvec_stream_kernel<FMT_Q4K, 2, true, false, false>), smem);
+        if (e == cudaSuccess) e = ensure_dynamic_smem(reinterpret_cast<const void*>(q4_matvec_stream_kernel<FMT_Q4K, 4, true, false, false>), smem);
+    }
+    return e;
 }
 
 size_t q4_prepared_x_bytes(uint32_t n_pos) { return (size_t)17 * ((n_pos + 7) & ~7u) * 16 + 128; }
@@ -930,6 +1128,7 @@ cudaError_t launch_q4_prepare_x(const XSource& src, void* image, float* plain_ou
     if (n_pos > 2048) return cudaErrorInvalidValue;   // 32 partial sums of 64 positions each
     PrepareParams p{};
     p.x = src.x, p.x2 = src.x2, p.x_pairs = src.x_pairs, p.x2_pairs = src.x2_pairs, p.epoch_ptr = src.epoch_ptr;
+    p.parity_stride = src.parity_stride_bytes;
     p.image = reinterpret_cast<uint4*>(image), p.plain_out = plain_out, p.status = status;
     p.n_pos = n_pos, p.pitch = (n_pos + 7) & ~7u, p.overlap = overlap ? 1u : 0u;
     cudaLaunchConfig_t cfg{};

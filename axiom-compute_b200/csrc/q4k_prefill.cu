@@ -159,10 +159,12 @@ q4k_prefill_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_consta
                    float* __restrict__ c, uint32_t m_total, uint32_t n_rows, uint32_t n_sb, uint32_t* status,
                    uint32_t independent) {
     // Programmatic dependent launch: the next launch may be scheduled onto SMs this grid leaves
-    // idle (112 CTAs on 148 SMs).  Unless the caller declared this call independent of the one
-    // before it (inputs not produced, C not read by it), nothing is read before that call is done.
-    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    // idle.  Unless the caller declared this call independent of the one before it (inputs not
+    // produced, C not read by it), nothing is read before that call is done, and the next launch is
+    // let through only after that wait: a launch scheduled behind an ordered one may read its
+    // inputs at once and must find every earlier launch of the stream complete.
     if (!independent) asm volatile("griddepcontrol.wait;" ::: "memory");
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     extern __shared__ uint8_t smem_dyn[];
     const uint32_t raw_addr = smem_u32(smem_dyn);
     const uint32_t base = (raw_addr + 1023u) & ~1023u;   // the swizzled tiles need 1024-byte alignment

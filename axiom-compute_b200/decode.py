@@ -86,6 +86,16 @@ def synth_chunk(rows: int, n_sb: int, seed: int, device) -> torch.Tensor:
     return q.view(-1)
 
 
+def full_matrix(shape: SweepShape, seed: int, layer: int, j: int, device) -> torch.Tensor:
+    """The whole matrix of linear j of `layer` (all row chunks), as ``DecodeSweep`` generates it."""
+    _n, rows, k = shape.linears[j]
+    return torch.cat([synth_chunk(rows // CHUNKS, k // 256, seed + (layer * 4 + j) * CHUNKS + c, device)
+                      for c in range(CHUNKS)])
+
+
+MODES = ("prepared", "fused", "poll", "mixed")
+
+
 class DecodeSweep:
     """One rank's share of the stack plus the buffers and launches of a token."""
 
@@ -95,10 +105,10 @@ class DecodeSweep:
             multi = torch.distributed.is_available() and torch.distributed.is_initialized() \
                 and torch.distributed.get_world_size(group) > 1
             mode = "fused" if multi else "mixed"
-        if mode not in ("prepared", "fused", "poll", "mixed"):
-            raise ValueError("mode must be 'prepared', 'fused', 'poll' or 'mixed'")
+        if mode not in MODES:
+            raise ValueError(f"mode must be one of {MODES}")
         self.shape, self.device = shape, torch.device(device)
-        self.mode = mode
+        self.mode, self.seed = mode, int(seed)
         self.consumer_polls = mode == "poll"
         self.world, self.rank = 1, 0
         self.tuning = tuning
@@ -110,6 +120,8 @@ class DecodeSweep:
             self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
         if CHUNKS % self.world:
             raise ValueError(f"world size must divide {CHUNKS}")
+        self.parallelism = (f"rows of every linear sharded over {self.world} GPUs, all-gather fused into the "
+                            "producer's epilogue (peer stores of (value, epoch) words)")
         for _n, rows, k in shape.linears:
             if rows % CHUNKS or k % 256 or k // 256 > 128:
                 raise ValueError("every linear needs rows divisible by 8 and K a multiple of 256 up to 32768")
@@ -133,6 +145,7 @@ class DecodeSweep:
                 o.append(off)
                 off += rows
             self.offsets.append(o)
+        self.checkable_outputs = (0, 1, 2, 3)   # linears whose full output vector every rank holds
         self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
         self.epoch = torch.zeros(1, dtype=torch.int32, device=self.device)
         self.h = torch.zeros(shape.hidden, dtype=torch.float32, device=self.device)     # token input (plain)
@@ -140,7 +153,11 @@ class DecodeSweep:
         if self.world > 1:
             import torch.distributed as dist
             import torch.distributed._symmetric_memory as symm_mem
-            self.pairs = symm_mem.empty(words, dtype=torch.int64, device=self.device)
+            # Two copies of the (value, epoch) store, used alternately by even and odd tokens: a rank
+            # that is already writing token t + 1 never touches words that a slower rank is still
+            # reading for token t.  (Token t + 2 cannot start anywhere before every rank has sent its
+            # last vector of token t + 1, which it does after it has read all of token t.)
+            self.pairs = symm_mem.empty(2 * words, dtype=torch.int64, device=self.device)
             self.pairs.zero_()
             self._handle = symm_mem.rendezvous(self.pairs, group)
             ptrs = list(self._handle.buffer_ptrs)
@@ -149,6 +166,7 @@ class DecodeSweep:
             self.ptr_table = torch.tensor(ptrs, dtype=torch.int64, device=self.device)
         else:
             self.pairs = None
+        self.parity_stride = words * 8
         self.vec = torch.zeros(words, dtype=torch.float32, device=self.device)
         if self.world == 1 and self.consumer_polls:
             raise ValueError("mode 'poll' needs more than one rank")
@@ -185,13 +203,13 @@ class DecodeSweep:
         tn = C.byref(self.tuning) if self.tuning is not None else None
         if self.world > 1:
             g = _ffi.AxcGather(self.ptr_table.data_ptr(), off * 8, self.epoch.data_ptr(), self.world, self.rank,
-                               self.rank * rows_local)
+                               self.rank * rows_local, self.parity_stride)
             rc = _ffi.lib().axc_cuda_q4k_matvec_fused(w.data_ptr(), C.byref(xsrc), None, rows_local, k // 256,
                                                       C.byref(g), self._stream(), st, tn)
             if rc == 0 and self.finish_after[j]:
                 rc = _ffi.lib().axc_cuda_gather_finish(
                     self.pairs.data_ptr() + off * 8, self.epoch.data_ptr(), self.vec.data_ptr() + off * 4, rows,
-                    self._stream(), st, _ffi.AXC_FINISH_OVERLAP_PREVIOUS)
+                    self._stream(), st, _ffi.AXC_FINISH_OVERLAP_PREVIOUS, self.parity_stride, None)
         else:
             rc = _ffi.lib().axc_cuda_q4k_matvec_fused(w.data_ptr(), C.byref(xsrc), self.vec.data_ptr() + off * 4,
                                                       rows_local, k // 256, None, self._stream(), st, tn)
@@ -212,13 +230,13 @@ class DecodeSweep:
                                             _ffi.AXC_FINISH_OVERLAP_PREVIOUS if overlap else 0))
         if self.world > 1:
             g = _ffi.AxcGather(self.ptr_table.data_ptr(), off * 8, self.epoch.data_ptr(), self.world, self.rank,
-                               self.rank * rows_local)
+                               self.rank * rows_local, self.parity_stride)
             rc = L.axc_cuda_q4k_matvec_prepared(w.data_ptr(), img, 1 if rms else 0, None, rows_local, k // 256,
                                                 C.byref(g), self._stream(), st, tn)
             if rc == 0 and self.finish_after[j]:
                 rc = L.axc_cuda_gather_finish(self.pairs.data_ptr() + off * 8, self.epoch.data_ptr(),
                                               self.vec.data_ptr() + off * 4, rows, self._stream(), st,
-                                              _ffi.AXC_FINISH_OVERLAP_PREVIOUS)
+                                              _ffi.AXC_FINISH_OVERLAP_PREVIOUS, self.parity_stride, None)
         else:
             rc = L.axc_cuda_q4k_matvec_prepared(w.data_ptr(), img, 1 if rms else 0,
                                                 self.vec.data_ptr() + off * 4, rows_local, k // 256, None,
@@ -233,10 +251,10 @@ class DecodeSweep:
             p = self.pairs.data_ptr()
             return _ffi.AxcXSrc(None, None, p + base * 8,
                                 None if second is None else p + (self.offsets[layer][j] + second) * 8,
-                                self.epoch.data_ptr(), 1 if rms else 0)
+                                self.epoch.data_ptr(), 1 if rms else 0, self.parity_stride)
         p = self.vec.data_ptr()
         return _ffi.AxcXSrc(p + base * 4, None if second is None else p + (self.offsets[layer][j] + second) * 4,
-                            None, None, None, 1 if rms else 0)
+                            None, None, None, 1 if rms else 0, 0)
 
     # -- one token --------------------------------------------------------------------------
     def token(self, normalise_input: bool = True) -> None:
@@ -252,7 +270,7 @@ class DecodeSweep:
             ov = False
             for layer in range(sh.layers):
                 if layer == 0:
-                    x = _ffi.AxcXSrc(self.h.data_ptr(), None, None, None, None, 1 if normalise_input else 0)
+                    x = _ffi.AxcXSrc(self.h.data_ptr(), None, None, None, None, 1 if normalise_input else 0, 0)
                 else:
                     x = self._src(layer - 1, 3)                         # h = unitRMS(d of the layer before)
                 sources = (x,                                            # q, k, v = W h
@@ -270,7 +288,8 @@ class DecodeSweep:
                 # some vectors were never unpacked: every vector (k and v included) in one pass
                 _raise_for(_ffi.lib().axc_cuda_gather_finish(
                     self.pairs.data_ptr(), self.epoch.data_ptr(), self.vec.data_ptr(),
-                    sh.vector_words_per_layer * sh.layers, self._stream(), self.status.data_ptr(), 0))
+                    sh.vector_words_per_layer * sh.layers, self._stream(), self.status.data_ptr(), 0,
+                    self.parity_stride, None))
             self.d_last.copy_(self.vec[last:last + sh.hidden])
 
     def _plain_store(self) -> torch.Tensor:

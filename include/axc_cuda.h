@@ -208,11 +208,17 @@ typedef struct axc_tuning {
     int32_t threads;
     int32_t evict_first; /* -1 = default */
     int32_t pdl;         /* programmatic dependent launch: 0 off, 1 on, 2 on with the weight
-                            stream started before the dependency wait (default), 3 = as 2 and the
-                            caller asserts that x is not written and y neither read nor written
-                            by the previous launch on this stream: only the final store of y
-                            waits for that launch, and the launch is shaped to overlap its
-                            neighbours (one small CTA per SM, up to four launches resident) */
+                            stream started before the dependency wait (default: an ORDERED
+                            launch, which lets the launch behind it be scheduled only after its
+                            own wait, i.e. once everything before it in the stream is complete),
+                            3 = an INDEPENDENT launch: the caller asserts that x is not written,
+                            and y neither read nor written, by any launch of this stream that may
+                            still be in flight, which is every launch from the most recent ordered
+                            one (inclusive; any kernel not of this library counts as ordered) up
+                            to this call.  Only the final store of y waits for the launch before,
+                            and the launch is shaped to overlap its neighbours (one small CTA per
+                            SM, up to four launches resident).  Example: producer of x, gate
+                            projection (pdl 2), up projection of the same x (pdl 3). */
     int32_t resident;    /* CTAs per SM the shared-memory budget is cut for; 0 = default */
 } axc_tuning;
 
@@ -250,13 +256,19 @@ int axc_cuda_q4_0_dequant(const void* q, float* w, uint32_t rows, uint32_t n_blo
  *   y_offset_bytes: where this call's vector (8 bytes per global row) starts in that storage;
  *   epoch: this rank's epoch counter (one device uint32, zero before first use), advanced by
  *     axc_cuda_gather_next_epoch once per step (one step = one pass over the vectors in use).
- * All ranks issue the same sequence of calls.  A vector may be rewritten once every rank has
- * finished the step that read it; a caller that cannot guarantee that alternates two vectors. */
+ * All ranks issue the same sequence of calls.  A vector may be rewritten only once every rank has
+ * finished the step that read it.  Nothing in the producer waits for that, so a caller whose ranks
+ * can drift apart by a step keeps TWO copies of the storage, parity_stride_bytes apart (0 = one
+ * copy): every kernel of this family then uses the copy selected by the low bit of the epoch it
+ * read, and the end-of-step handshake of axc_cuda_gather_finish (axc_gather_sync) keeps any rank
+ * from starting step e + 2 before every rank has consumed step e.  A reader that meets a word
+ * from a LATER epoch than its own sets bit 8 of *status instead of accepting it. */
 typedef struct axc_gather {
     const uint64_t* y_peer_bases;
     uint64_t y_offset_bytes;
     const uint32_t* epoch;
     uint32_t world, rank, row_offset;
+    uint64_t parity_stride_bytes;
 } axc_gather;
 int axc_cuda_q4k_matvec_allgather(const void* q, const float* x, uint32_t rows_local,
                                   uint32_t n_superblocks, const axc_gather* g, void* stream,
@@ -276,9 +288,10 @@ int axc_cuda_q4k_prefill(const void* q, const uint16_t* a_bf16, float* c, uint32
 /* The same with the kernel form chosen by the caller: 0 = the library's choice, 1 = one CTA per
  * 128-row tile (tcgen05.mma.cta_group::1), 2 = a pair of CTAs per 256 rows (cta_group::2).
  * flags: AXC_PREFILL_INDEPENDENT = the caller states that q and a are not written, and c not read
- * or written, by the launch directly before this one in the stream (say the up projection right
- * after the gate projection of the same activations): the call may then start on SMs the previous
- * call leaves idle (a 14336-row matrix is 112 tiles on 148 SMs); only its stores of c wait. */
+ * or written, by any launch of the stream from the most recent one made without this flag
+ * (inclusive) up to this call (say the up projection right after the gate projection of the same
+ * activations): the call may then start on SMs the previous call leaves idle; only its stores of
+ * c wait.  A call without the flag lets the next launch be scheduled only after its own wait. */
 #define AXC_PREFILL_INDEPENDENT 1u
 int axc_cuda_q4k_prefill_form(const void* q, const uint16_t* a_bf16, float* c, uint32_t m_tokens,
                               uint32_t n_rows, uint32_t n_superblocks, void* stream, uint32_t* status, int form,
@@ -300,6 +313,7 @@ typedef struct axc_xsrc {
     const uint64_t* x2_pairs;
     const uint32_t* epoch;
     uint32_t unit_rms;
+    uint64_t parity_stride_bytes; /* (value, epoch) sources: distance of the odd-epoch copy, 0 = one copy */
 } axc_xsrc;
 int axc_cuda_q4k_matvec_fused(const void* q, const axc_xsrc* xs, float* y, uint32_t rows,
                               uint32_t n_superblocks, const axc_gather* g, void* stream,
@@ -322,12 +336,28 @@ int axc_cuda_q4k_matvec_prepared(const void* q, const void* image, uint32_t unit
                                  const axc_tuning* tuning);
 /* *epoch += 1, in stream order (a one-thread kernel). */
 int axc_cuda_gather_next_epoch(uint32_t* epoch, void* stream);
-/* Consumer side: pairs = this rank's own pair storage (n words), out = n fp32 values.
+/* Consumer side: pairs = this rank's own pair storage (n words; the copy for odd epochs
+ * parity_stride_bytes further on when that is non-zero), out = n fp32 values.
  * flags: AXC_FINISH_OVERLAP_PREVIOUS lets the kernel start before the launch directly before it
  * in the stream has completed (it polls for that launch's words anyway); the caller guarantees
- * that launch neither advances the epoch nor reads or writes `out`. */
+ * that launch neither advances the epoch nor reads or writes `out`.
+ * sync (nullable): the end-of-step handshake for callers whose ranks are not kept in step by the
+ * data they exchange.  The last CTA of the launch stores the epoch it consumed into entry `rank`
+ * of every rank's done array (a peer store), waits (bounded, then bit 4 of *status) until its own
+ * done array shows that every rank has consumed the epoch before, and only then advances *epoch
+ * itself: the caller issues no axc_cuda_gather_next_epoch.  With two copies of the storage this
+ * makes the reuse of a copy two steps later safe.  The epoch counter starts at 1 for this
+ * protocol; done arrays and arrive_counter are zero before first use.  n may be 0 (handshake only). */
+typedef struct axc_gather_sync {
+    const uint64_t* done_peer_bases; /* DEVICE array of `world` addresses: each rank's uint32 done[world] */
+    const uint32_t* done_local;      /* this rank's own done[world] */
+    uint32_t* arrive_counter;        /* one device uint32 of scratch */
+    uint32_t* epoch;                 /* the epoch counter, read and advanced */
+    uint32_t world, rank;
+} axc_gather_sync;
 int axc_cuda_gather_finish(const uint64_t* pairs, const uint32_t* epoch, float* out, uint32_t n,
-                           void* stream, uint32_t* status, uint32_t flags);
+                           void* stream, uint32_t* status, uint32_t flags, uint64_t parity_stride_bytes,
+                           const axc_gather_sync* sync);
 
 /* Launch geometry the matvec launchers would use (no launch). */
 int axc_cuda_q4k_matvec_plan(uint32_t rows, uint32_t n_superblocks, const axc_tuning* tuning,
@@ -346,8 +376,15 @@ int axc_cuda_q4k_matvec_plan(uint32_t rows, uint32_t n_superblocks, const axc_tu
  * that device current and before any stream capture begins.  All calls on a device share the
  * one array: calls whose kernels could overlap on the GPU (different streams) race on it and
  * must be ordered by the caller; calls in one stream are safe, each call rewrites every word it
- * later reads.  No cudaMalloc, cudaFree or allocating library routine is called. */
+ * later reads.  The entry point itself calls no cudaMalloc, cudaFree or allocating library
+ * routine; but the CUDA runtime loads a kernel (and the module that holds the array) the first
+ * time it is used on a device, and that load may allocate device memory and synchronise.  Call
+ * axc_cuda_q4k_matvec_static_warmup() once per device at start-up, with that device current and
+ * outside any stream capture: it looks up the array and loads every kernel this entry point can
+ * launch (the quantiser and the three tile heights of the matvec) without launching anything, so
+ * that later calls of any shape find everything resident. */
 #define AXC_STATIC_MAX_SUPERBLOCKS 128
+int axc_cuda_q4k_matvec_static_warmup(void);
 int axc_cuda_q4k_matvec_static(const void* q, const float* x, float* y, uint32_t rows,
                                uint32_t n_superblocks, void* stream);
 

@@ -17,10 +17,11 @@ def dev(a):
     return torch.from_numpy(np.ascontiguousarray(a)).cuda()
 
 
-def fused(ffi, q, rows, n_sb, x=None, x2=None, xp=None, x2p=None, epoch=None, rms=False, gather=None, y=None, st=None):
+def fused(ffi, q, rows, n_sb, x=None, x2=None, xp=None, x2p=None, epoch=None, rms=False, gather=None, y=None, st=None,
+          parity_stride=0):
     xs = ffi.AxcXSrc(x.data_ptr() if x is not None else None, x2.data_ptr() if x2 is not None else None,
                      xp.data_ptr() if xp is not None else None, x2p.data_ptr() if x2p is not None else None,
-                     epoch.data_ptr() if epoch is not None else None, 1 if rms else 0)
+                     epoch.data_ptr() if epoch is not None else None, 1 if rms else 0, parity_stride)
     rc = ffi.lib().axc_cuda_q4k_matvec_fused(q.data_ptr(), C.byref(xs), y.data_ptr() if y is not None else None,
                                              rows, n_sb, C.byref(gather) if gather is not None else None,
                                              int(torch.cuda.current_stream().cuda_stream),
@@ -57,12 +58,13 @@ def test_fused_source_reads_epoch_words_and_chains(ffi, ops, synth):
     pg = coll.PeerGather(2 * ffn, 1, "cuda")
     st = ops.new_status()
     y = torch.empty(hid, device="cuda")
-    for it in range(2):
-        pg.begin_step()
+    for it in range(3):
         pg.matvec(dev(gu_w), dev(x), hid // 256, 0, status=st)
         pairs = pg.pairs
         second = pairs[ffn:]
-        assert fused(ffi, dev(dn_w), hid, ffn // 256, xp=pairs, x2p=second, epoch=pg.epoch, rms=True, y=y, st=st) == 0
+        assert fused(ffi, dev(dn_w), hid, ffn // 256, xp=pairs, x2p=second, epoch=pg.epoch, rms=True, y=y, st=st,
+                     parity_stride=pg.parity_stride) == 0
+        pg.finish(st)     # ends the step: the next one writes the other copy
         torch.cuda.synchronize()
         assert int(st.item()) == 0
         gu = oracle.matvec_rows("q4k", gu_w, x, 2 * ffn, hid // 256)
@@ -106,16 +108,20 @@ def test_gather_finish_overlapping_its_producer(ffi, ops, synth):
     pg = coll.PeerGather(rows, 1, "cuda")
     st = ops.new_status()
     out = torch.zeros(rows, device="cuda")
+    s = int(torch.cuda.current_stream().cuda_stream)
     for it in range(3):
-        pg.begin_step()
         pg.matvec(q, x, n_sb, 0, status=st)
         rc = ffi.lib().axc_cuda_gather_finish(pg.pairs.data_ptr(), pg.epoch.data_ptr(), out.data_ptr(), rows,
-                                              int(torch.cuda.current_stream().cuda_stream), st.data_ptr(),
-                                              ffi.AXC_FINISH_OVERLAP_PREVIOUS)
+                                              s, st.data_ptr(), ffi.AXC_FINISH_OVERLAP_PREVIOUS, pg.parity_stride, None)
         assert rc == 0
         y = ops.q4k_matvec(q, x, rows, n_sb)
         assert torch.equal(out, y)
         out.zero_()
+        assert ffi.lib().axc_cuda_gather_next_epoch(pg.epoch.data_ptr(), s) == 0
+    # the end-of-step handshake advances the epoch, so it may not run ahead of the launch before it
+    assert ffi.lib().axc_cuda_gather_finish(pg.pairs.data_ptr(), pg.epoch.data_ptr(), out.data_ptr(), rows, s,
+                                            st.data_ptr(), ffi.AXC_FINISH_OVERLAP_PREVIOUS, pg.parity_stride,
+                                            C.byref(pg._sync)) == 100
     assert int(st.item()) == 0
 
 
@@ -137,7 +143,7 @@ def test_prepared_x_matches_oracle(ffi, ops, synth, rows, n_sb, second, rms):
     y = torch.empty(rows, device="cuda")
     st = ops.new_status()
     ad, bd, qd = dev(a), dev(b), dev(q)
-    xs = ffi.AxcXSrc(ad.data_ptr(), bd.data_ptr() if second else None, None, None, None, 0)
+    xs = ffi.AxcXSrc(ad.data_ptr(), bd.data_ptr() if second else None, None, None, None, 0, 0)
     s = int(torch.cuda.current_stream().cuda_stream)
     for _ in range(2):
         assert L.axc_cuda_q4k_prepare_x(C.byref(xs), img.data_ptr(), plain.data_ptr(), n_sb, s, st.data_ptr(), 0) == 0
@@ -155,11 +161,11 @@ def test_prepare_x_argument_checks(ffi, synth):
     pairs = torch.zeros(256, dtype=torch.int64, device="cuda")
     img = torch.zeros(int(L.axc_cuda_q4k_prepared_x_bytes(1)), dtype=torch.uint8, device="cuda")
     s = int(torch.cuda.current_stream().cuda_stream)
-    plain_src = ffi.AxcXSrc(x.data_ptr(), None, None, None, None, 0)
+    plain_src = ffi.AxcXSrc(x.data_ptr(), None, None, None, None, 0, 0)
     assert L.axc_cuda_q4k_prepare_x(C.byref(plain_src), None, None, 1, s, None, 0) == 100
     assert L.axc_cuda_q4k_prepare_x(C.byref(plain_src), img.data_ptr(), None, 129, s, None, 0) == 100
     assert L.axc_cuda_q4k_prepare_x(C.byref(plain_src), img.data_ptr(), None, 1, s, None, 1) == 100   # plain source may not overlap
-    no_epoch = ffi.AxcXSrc(None, None, pairs.data_ptr(), None, None, 0)
+    no_epoch = ffi.AxcXSrc(None, None, pairs.data_ptr(), None, None, 0, 0)
     assert L.axc_cuda_q4k_prepare_x(C.byref(no_epoch), img.data_ptr(), None, 1, s, None, 0) == 100
     assert L.axc_cuda_q4k_prepared_x_bytes(16) == 17 * 64 * 16 + 128
 

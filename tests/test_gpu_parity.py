@@ -211,8 +211,8 @@ def test_q4k_ring_refill_path(ops, synth):
 
 def test_q4k_fused_allgather_epilogue_single_rank(synth):
     """The all-gather epilogue with world = 1 (peer table = own buffer): every slice lands at the
-    row offset of its slot as (value, epoch) words, finish() unpacks exactly the plain matvec's
-    values, and epochs advance per step."""
+    row offset of its slot as (value, epoch) words in the copy of the step's parity, finish()
+    unpacks exactly the plain matvec's values and ends the step (epoch advanced, done word set)."""
     from conftest import load_pkg
     coll = load_pkg("collective")
     ops_ = load_pkg("ops")
@@ -220,8 +220,10 @@ def test_q4k_fused_allgather_epilogue_single_rank(synth):
     pg = coll.PeerGather(rows, slots, "cuda")
     assert (pg.world, pg.rank, pg.row_offset, pg.rows_local) == (1, 0, 0, rows)
     st = ops_.new_status()
-    for it in range(2):
-        pg.begin_step()
+    n = rows * slots
+    for it in range(3):
+        epoch = it + 1
+        assert int(pg.epoch.item()) == epoch
         cases = []
         for slot in range(slots):
             q = synth.q4k_weights(rows, n_sb, 4000 + 10 * it + slot)
@@ -237,8 +239,13 @@ def test_q4k_fused_allgather_epilogue_single_rank(synth):
             y_ref = oracle.matvec_rows("q4k", q, x, rows, n_sb)
             _y64, mag = oracle.matvec_rows_f64("q4k", q, x, rows, n_sb)
             assert (np.abs(y.cpu().numpy() - y_ref) / mag).max() <= NORMWISE_TOL
-        assert int(pg.epoch.item()) == it + 1
-        assert ((pg.pairs.cpu().numpy() >> 32) == it + 1).all()    # every word carries the step's epoch
+        assert int(pg.epoch.item()) == epoch + 1                   # finish ended the step
+        words = pg.pairs.cpu().numpy()
+        copy = words[(epoch & 1) * n:(epoch & 1) * n + n]
+        assert ((copy >> 32) == epoch).all()                       # every word carries the step's epoch
+        other = words[(1 - (epoch & 1)) * n:(1 - (epoch & 1)) * n + n]
+        assert ((other >> 32) == max(epoch - 1, 0)).all()          # the other copy still holds the step before
+        assert int(words[2 * n:].view(np.int32)[0]) == epoch       # this rank's done word
     assert int(st.item()) == 0
 
 
@@ -248,13 +255,29 @@ def test_gather_finish_times_out_without_faulting():
     from conftest import load_pkg
     coll = load_pkg("collective")
     ops_ = load_pkg("ops")
-    pg = coll.PeerGather(8, 1, "cuda")
-    pg.begin_step()          # epoch 1, nothing stores
+    pg = coll.PeerGather(8, 1, "cuda")      # epoch 1, nothing stores
     st = ops_.new_status()
     pg.finish(st)
     torch.cuda.synchronize()
     assert int(st.item()) & 4
     assert torch.zeros(4, device="cuda").sum().item() == 0.0
+
+
+def test_gather_finish_reports_a_word_from_a_later_epoch():
+    """A producer that ran ahead of the reader (storage reused too early) is reported, not
+    accepted: a word of epoch 3 in the copy that epoch 1 reads sets bit 8."""
+    from conftest import load_pkg
+    coll = load_pkg("collective")
+    ops_ = load_pkg("ops")
+    pg = coll.PeerGather(8, 1, "cuda")
+    words = torch.full((8,), (1 << 32) | 0x3F800000, dtype=torch.int64, device="cuda")
+    words[5] = (3 << 32) | 0x40000000
+    pg.pairs[8:16] = words                  # epoch 1 is odd: second copy
+    st = ops_.new_status()
+    pg.finish(st)
+    torch.cuda.synchronize()
+    assert int(st.item()) == 8
+    assert pg.vector(0)[0].item() == 1.0
 
 
 # ---------------------------------------------------------------------------------- Q4_0
@@ -312,16 +335,23 @@ def test_q4_0_zero_blocks_writes_positive_zero(ops):
 
 # ------------------------------------------------------------------- full benchmark sizes
 
-def _full_size_check(ops, fmt, q_np, x_np, rows, n, sample_rows):
+def _full_size_check(ops, fmt, q_np, x_np, rows, n, sample_rows, tuning=None, calls=1):
     """Full-size run: every row against an fp64 product of the GPU's own bit-exact dequantised
-    weights (themselves checked against the oracle on a row sample), the oracle on the sample."""
+    weights (themselves checked against the oracle on a row sample), the oracle on the sample.
+    `calls` back-to-back launches with `tuning` (each into its own y; all must agree bit for bit)."""
     q, x = dev(q_np), dev(x_np)
     blk_b, blk_e = (144, 256) if fmt == "q4k" else (18, 32)
-    matvec = ops.q4k_matvec if fmt == "q4k" else ops.q4_0_matvec
+    matvec_ = ops.q4k_matvec if fmt == "q4k" else ops.q4_0_matvec
+    matvec = lambda *a, **kw: matvec_(*a, tuning=tuning, **kw)
     dequant = ops.q4k_dequant if fmt == "q4k" else ops.q4_0_dequant
     st = ops.new_status()
-    y = matvec(q, x, rows, n, status=st)
+    ys = [torch.full((rows,), float("nan"), dtype=torch.float32, device="cuda") for _ in range(calls)]
+    for yy in ys:
+        matvec(q, x, rows, n, y=yy, status=st)
+    y = ys[0]
     assert int(st.item()) == 0
+    for yy in ys[1:]:
+        assert torch.equal(yy, y)
     w = dequant(q, rows, n)
     for r in sample_rows:
         w_ref = oracle.dequant_rows(fmt, q_np[r * n * blk_b:(r + 1) * n * blk_b], 1, n)[0]
@@ -366,3 +396,135 @@ def test_q4_0_full_size_4096x4096(ops, synth):
     q = synth.q4_0_weights(rows, n, synth.config_seed(1, 0))
     x = synth.activations(n * 32, synth.config_seed(1, 1))
     _full_size_check(ops, "q4_0", q, x, rows, n, [0, 13, 14, 2048, 4095])
+
+
+@pytest.mark.parametrize("shape", ["up_gate_14336x4096", "down_4096x14336", "q4_0_4096x4096"])
+def test_full_size_under_the_benchmark_launch_geometry(ops, synth, shape):
+    """The geometry the benchmark times: calls declared independent (pdl = 3: one small CTA per SM,
+    several launches resident), three launches back to back, every row checked."""
+    tn = ops.make_tuning(pdl=3)
+    if shape == "up_gate_14336x4096":
+        rows, n, fmt = 14336, 16, "q4k"
+        q, x = synth.q4k_weights(rows, n, synth.config_seed(2, 0)), synth.activations(n * 256, synth.config_seed(2, 1))
+    elif shape == "down_4096x14336":
+        rows, n, fmt = 4096, 56, "q4k"
+        q, x = synth.q4k_weights(rows, n, synth.config_seed(2, 2)), synth.activations(n * 256, synth.config_seed(2, 3))
+    else:
+        rows, n, fmt = 4096, 128, "q4_0"
+        q, x = synth.q4_0_weights(rows, n, synth.config_seed(1, 0)), synth.activations(n * 32, synth.config_seed(1, 1))
+    y3 = _full_size_check(ops, fmt, q, x, rows, n, [0, 1, rows // 2, rows - 1], tuning=tn, calls=3)
+    # and the same values as the ordered geometry delivers
+    y2 = (ops.q4k_matvec if fmt == "q4k" else ops.q4_0_matvec)(dev(q), dev(x), rows, n, tuning=ops.make_tuning(pdl=2))
+    assert torch.equal(y3, y2)
+
+
+def test_independent_launch_behind_an_ordered_one_sees_the_producer(ops, synth):
+    """producer matvec -> ordered matvec (pdl 2) -> independent matvec (pdl 3), both consumers
+    reading the producer's y as their x.  The independent launch reads x without waiting; the
+    ordered launch in between lets it be scheduled only after its own wait, i.e. when the producer
+    is complete, so both consumers must match the oracle on the oracle's own intermediate."""
+    k0, mid, rows = 4096, 4096, 3000
+    wp = synth.q4k_weights(mid, k0 // 256, 9101)
+    wg = synth.q4k_weights(rows, mid // 256, 9102)
+    wu = synth.q4k_weights(rows, mid // 256, 9103)
+    x0 = synth.activations(k0, 9104)
+    wpd, wgd, wud, x0d = dev(wp), dev(wg), dev(wu), dev(x0)
+    v = torch.zeros(mid, device="cuda")
+    yg, yu = torch.zeros(rows, device="cuda"), torch.zeros(rows, device="cuda")
+    st = ops.new_status()
+    for it in range(5):
+        v.zero_()     # a consumer that ran ahead of the producer would read zeros
+        ops.q4k_matvec(wpd, x0d, mid, k0 // 256, y=v, status=st, tuning=ops.make_tuning(pdl=2))
+        ops.q4k_matvec(wgd, v, rows, mid // 256, y=yg, status=st, tuning=ops.make_tuning(pdl=2))
+        ops.q4k_matvec(wud, v, rows, mid // 256, y=yu, status=st, tuning=ops.make_tuning(pdl=3))
+        torch.cuda.synchronize()
+        assert int(st.item()) == 0
+        v_np = v.cpu().numpy()
+        check_fast("q4k", v_np, wp, x0, mid, k0 // 256)
+        check_fast("q4k", yg.cpu().numpy(), wg, v_np, rows, mid // 256)
+        check_fast("q4k", yu.cpu().numpy(), wu, v_np, rows, mid // 256)
+
+
+def _log_uniform_x(k, spread_bits, seed):
+    """|x| log-uniform over 2^0 .. 2^-spread_bits with random signs, independently per element, so
+    every 64-column chunk holds the whole range (the fixed-point scale is per chunk)."""
+    rng = np.random.default_rng(seed)
+    return (np.exp2(-rng.uniform(0.0, spread_bits, k)) * rng.choice([-1.0, 1.0], k)).astype(np.float32)
+
+
+@pytest.mark.parametrize("fmt,rows,n", [("q4k", 512, 16), ("q4k", 64, 112), ("q4_0", 512, 128)])
+@pytest.mark.parametrize("spread_bits", [10, 30])
+def test_magnitudes_spread_inside_every_chunk(ops, synth, fmt, rows, n, spread_bits):
+    """Activations whose magnitudes span up to 2^30 INSIDE each 64-column chunk: elements below
+    2^-24 of their chunk's maximum are flushed by the fixed point.  Observed norm-wise maximum
+    against the oracle: below 1e-6 (a numpy model of the fixed point alone gives 6e-8; the rest is
+    the summation-order difference to the fp32-sequential reference, about 3e-7)."""
+    blk_e = 256 if fmt == "q4k" else 32
+    q = (synth.q4k_weights if fmt == "q4k" else synth.q4_0_weights)(rows, n, 9200 + n)
+    x = _log_uniform_x(n * blk_e, spread_bits, 9300 + spread_bits)
+    y = (ops.q4k_matvec if fmt == "q4k" else ops.q4_0_matvec)(dev(q), dev(x), rows, n).cpu().numpy()
+    y_ref = oracle.matvec_rows(fmt, q, x, rows, n)
+    y64, mag = oracle.matvec_rows_f64(fmt, q, x, rows, n)
+    assert (np.abs(y - y_ref) / mag).max() <= 1e-6
+    assert (np.abs(y - y64) / mag).max() <= 1e-6       # and as close to exact arithmetic
+
+
+def test_fixed_point_worst_case_stays_inside_its_derived_bound(ops, synth):
+    """The adversarial input for a per-chunk fixed point: in every chunk one element at 1.0 placed
+    where that row's |w| is smallest, the other 63 at 1.4 * 2^-24 (just above half a unit of the
+    fixed point: they round to one unit, an error of 0.3 units each).  Relative to sum |w_i x_i| the
+    error is then no longer small, which the derivation beside X_FRAC_BITS says; what must hold is
+    the derived absolute bound  |dy| <= 2^-23 * sum_chunks M_c * sum_{i in c} |w_i|  (plus the fp32
+    rounding of the row sum)."""
+    rows, n = 8, 16
+    q = synth.q4k_weights(rows, n, 9400)
+    w = oracle.dequant_rows("q4k", q, rows, n).astype(np.float64)
+    qd = dev(q)
+    for r in range(rows):
+        x = np.full(n * 256, 1.4 * 2.0 ** -24, np.float32)
+        for c in range(0, n * 256, 64):
+            x[c + int(np.argmin(np.abs(w[r, c:c + 64])))] = 1.0
+        y = ops.q4k_matvec(qd, dev(x), rows, n).cpu().numpy()[r]
+        exact = float(w[r] @ x.astype(np.float64))
+        bound = 2.0 ** -23 * np.abs(w[r]).sum() + 1e-6 * float(np.abs(w[r]) @ np.abs(x.astype(np.float64)))
+        assert abs(float(y) - exact) <= bound, (r, y, exact, bound)
+
+
+def test_rows_whose_dequantised_weights_are_all_zero(ops, synth):
+    """Rows the reference computes as exactly 0.0 (every dequantised weight is 0), judged by its
+    own rule: |cpu| <= 1e-10, so the ABSOLUTE difference counts
+    (crates/axc-driver/tests/compile_q4km_dequant_matvec.rs:946-950).
+    Q4_0: all nibbles 8 -> (8 - 8) * d = 0; the kernel sums (q - 8) X in integers, so it returns
+    exactly 0 too.  Q4_K_M: d = dmin, every nibble q0 and sc * q0 = m, so d*sc*q0 - dmin*m = 0; the
+    kernel factors the sum as d*sc*sum(q X) - dmin*m*sum(X) over the same fixed-point X, which
+    cancels to rounding: a residual of a few 1e-7 of the cancelled magnitude, held to 1e-5 of it."""
+    # Q4_0
+    rows, n = 6, 128
+    q = synth.q4_0_weights(rows, n, 9500).reshape(rows, n, 18).copy()
+    q[2, :, 2:] = 0x88
+    q[5, :, 2:] = 0x88
+    x = synth.activations(n * 32, 9501) * np.float32(1000.0)
+    y = ops.q4_0_matvec(dev(q.reshape(-1)), dev(x), rows, n).cpu().numpy()
+    y_cpu = oracle.matvec_rows("q4_0", q.reshape(-1), x, rows, n)
+    assert y_cpu[2] == 0.0 and y_cpu[5] == 0.0
+    assert y[2] == 0.0 and y[5] == 0.0
+    keep = [0, 1, 3, 4]                # (a row of zero weights has no norm-wise figure)
+    _y64, mag = oracle.matvec_rows_f64("q4_0", q.reshape(-1), x, rows, n)
+    assert (np.abs(y[keep] - y_cpu[keep]) / mag[keep]).max() <= NORMWISE_TOL
+    # Q4_K_M
+    rows, n = 4, 16
+    qk = synth.q4k_weights(rows, n, 9502).reshape(rows, n, 144).copy()
+    sc, q0 = 5, 7                     # sc * q0 = 35 = m, both below 64
+    one = np.array([0.01], np.float16).view(np.uint8)
+    for sb in range(n):
+        qk[1, sb, 0:2] = one
+        qk[1, sb, 2:4] = one
+        qk[1, sb, 4:16] = synth.pack_q4k_scales(np.full(8, sc), np.full(8, sc * q0))
+        qk[1, sb, 16:] = q0 | (q0 << 4)
+    xk = synth.activations(n * 256, 9503)
+    yk = ops.q4k_matvec(dev(qk.reshape(-1)), dev(xk), rows, n).cpu().numpy()
+    yk_cpu = oracle.matvec_rows("q4k", qk.reshape(-1), xk, rows, n)
+    assert yk_cpu[1] == 0.0
+    cancelled = float(np.float32(one.view(np.float16)[0]) * sc * q0 * np.abs(xk).sum())
+    assert abs(float(yk[1])) <= 1e-5 * cancelled       # the reference's rule: absolute difference
+    assert abs(float(yk[1])) <= 1e-3                   # and inside the reference's own 1e-3 bar

@@ -60,3 +60,24 @@ def test_static_entry_point_rejects_rows_longer_than_its_scratch(ffi):
     assert _call_static(ffi, q, x, y, 1, 128) == ffi.AXC_OK      # the stated maximum works
     torch.cuda.synchronize()
     assert float(y.item()) == 0.0
+
+
+def test_static_entry_point_leaves_free_memory_unchanged_after_warmup(ffi, synth):
+    """After the start-up warm-up (array looked up, every kernel of the path loaded) calls of
+    different shapes, which take different tile heights of the matvec kernel, change nothing in
+    the device's free memory: neither the entry point nor the runtime allocates on its behalf."""
+    assert ffi.lib().axc_cuda_q4k_matvec_static_warmup() == ffi.AXC_OK
+    shapes = [(4096, 16), (16, 128), (3, 1), (1000, 56)]
+    bufs = []
+    for rows, n_sb in shapes:       # the caller's own buffers exist before the measurement
+        q = torch.from_numpy(synth.q4k_weights(rows, n_sb, 7300 + rows)).cuda()
+        x = torch.from_numpy(synth.activations(n_sb * 256, 7400 + rows)).cuda()
+        y = torch.zeros(rows, dtype=torch.float32, device="cuda")
+        bufs.append((q, x, y, rows, n_sb))
+    torch.cuda.synchronize()
+    free_before, _total = torch.cuda.mem_get_info()
+    for q, x, y, rows, n_sb in bufs:
+        assert _call_static(ffi, q, x, y, rows, n_sb) == ffi.AXC_OK
+    torch.cuda.synchronize()
+    free_after, _total = torch.cuda.mem_get_info()
+    assert free_after == free_before
