@@ -39,11 +39,22 @@ struct XSource {
 };
 
 // Completion signal of the streaming matvec for a host that polls a word in mapped host memory
-// instead of waiting on an event: the last CTA to finish writes `seq` to `flag` after every
-// store of y is visible to the host.  `counter` is one device word, zero before first use.
+// instead of waiting on an event: the last CTA to finish writes `seq` to `flag` once y is visible
+// to the host.  `counter` is one device word, zero before first use.
 struct DoneSignal {
     uint32_t* counter;
     uint32_t* flag;
+    uint32_t seq;
+    float* y_host;   // optional: y is device memory; the last CTA copies it here (mapped host memory) before `flag`
+};
+
+// Single-launch host dispatch: x lies in mapped host memory; the launch's first CTAs quantise it
+// into the image named by MatvecTuning::x_prepared and publish `seq` in `ready` (device words,
+// zero before first use), which all CTAs wait for (bounded) before reading the image.
+struct HostX {
+    const float* x_host;   // device view of the mapped host buffer
+    uint32_t* ready;
+    uint32_t* counter;
     uint32_t seq;
 };
 
@@ -62,6 +73,7 @@ struct MatvecTuning {
     const GatherArgs* gather = nullptr;  // all-gather fused into the epilogue (y is ignored)
     const XSource* xsrc = nullptr;       // fused activation source (Q4_K_M only; x is ignored)
     const DoneSignal* done = nullptr;    // completion signal for a polling host (streaming kernels only)
+    const HostX* host_x = nullptr;       // with x_prepared: the launch produces the image itself from host memory
 };
 
 // True when launch_q4k_matvec / launch_q4_0_matvec take the streaming kernel for this row length

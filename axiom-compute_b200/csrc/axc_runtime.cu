@@ -363,19 +363,25 @@ int dispatch_locked(axc_ctx* ctx, axc_kernel* k, const uint32_t wg[3], const voi
         }
     }
 
-    // ---- the fast path: no copy-engine transfer for x, no event ----
-    // x stays in its mapped staging buffer; one small kernel reads it over PCIe and quantises it
-    // once for all CTAs, the matvec (launched behind it with programmatic dependent launch, its
-    // weight stream already running) stores y straight into mapped host memory and its last CTA
-    // publishes a sequence number there, which this thread polls.  Taken whenever the streaming
-    // kernel serves the shape and no device timing was asked for.
-    const uint32_t n_pos = k->kind == KernelKind::Q4K ? n * 4u : n / 2u;
-    bool fast = !timed && rows > 0 && n > 0 && !k->strict.load() && sx.staging_dev && sy.mapped &&
-                !k->tune.x_prepared &&
+    // ---- the fast path: one launch, no copy-engine transfer for x, no event ----
+    // x stays in its mapped staging buffer; the matvec's first CTAs read it over PCIe and quantise
+    // it once for all CTAs (which meanwhile stream their weights), every CTA stores its rows of y
+    // straight into mapped host memory, and the last CTA publishes a sequence number there, which
+    // this thread polls.  Taken whenever the streaming kernel serves the shape and no device
+    // timing was asked for.
+    // (Inputs that are also read back take the copy path: x then has to be in device memory.)
+    static const bool fast_enabled = [] {
+        const char* v = std::getenv("AXC_DISPATCH_FAST");   // "0" forces the copy-and-event path
+        return !(v && v[0] == '0' && v[1] == '\0');
+    }();
+    bool fast = fast_enabled && !timed && rows > 0 && n > 0 && !k->strict.load() && sx.staging_dev && sy.mapped &&
+                output_sizes[0] == 0 && output_sizes[1] == 0 && !k->tune.x_prepared &&
+                rows >= 64 &&   // enough CTAs for one producer per 64 x 64 columns of x (at most eight)
                 (k->kind == KernelKind::Q4K ? axc::q4k_uses_stream_kernel(n) : axc::q4_0_uses_stream_kernel(n));
     if (fast && !k->fast_scratch) {
-        const size_t image = (axc::q4_prepared_x_bytes(512) + 255) & ~(size_t)255;   // rows of up to 32768 columns
-        if (cudaMalloc(&k->fast_scratch, image + 256) == cudaSuccess &&
+        // [quantised x image for rows of up to 32768 columns | 256 B of counters | y, up to the mapped-output limit]
+        const size_t image = (axc::q4_prepared_x_bytes(512) + 255) & ~(size_t)255;
+        if (cudaMalloc(&k->fast_scratch, image + 256 + kMappedOutputMax) == cudaSuccess &&
             cudaMemsetAsync((char*)k->fast_scratch + image, 0, 256, st) == cudaSuccess) {
             k->fast_image_bytes = image;
         } else {
@@ -409,20 +415,20 @@ int dispatch_locked(axc_ctx* ctx, axc_kernel* k, const uint32_t wg[3], const voi
                     ? axc::launch_q4k_matvec_seq((const uint8_t*)sq.dev, (const float*)sx.dev, (float*)sy.dev, (uint32_t)rows, n, st)
                     : axc::launch_q4_0_matvec_seq((const uint8_t*)sq.dev, (const float*)sx.dev, (float*)sy.dev, (uint32_t)rows, n, st);
         } else if (fast) {
-            axc::XSource src;
-            src.x = (const float*)sx.staging_dev;
-            e = axc::launch_q4_prepare_x(src, k->fast_scratch, nullptr, n_pos, k->status_dev, st, false);
-            if (e == cudaSuccess) {
-                seq = ++k->fast_seq;
-                if (seq == 0) seq = ++k->fast_seq;   // 0 is what a fresh flag word holds
-                axc::DoneSignal done{reinterpret_cast<uint32_t*>((char*)k->fast_scratch + k->fast_image_bytes), k->status_dev + 4, seq};
-                axc::MatvecTuning tune = k->tune;
-                tune.x_prepared = k->fast_scratch;
-                tune.done = &done;
-                e = k->kind == KernelKind::Q4K
-                        ? axc::launch_q4k_matvec((const uint8_t*)sq.dev, nullptr, (float*)sy.dev, (uint32_t)rows, n, k->status_dev, st, tune, k->sm_count, nullptr)
-                        : axc::launch_q4_0_matvec((const uint8_t*)sq.dev, nullptr, (float*)sy.dev, (uint32_t)rows, n, k->status_dev, st, tune, k->sm_count, nullptr);
-            }
+            seq = ++k->fast_seq;
+            if (seq == 0) seq = ++k->fast_seq;   // 0 is what fresh flag words hold
+            uint32_t* words = reinterpret_cast<uint32_t*>((char*)k->fast_scratch + k->fast_image_bytes);
+            float* y_dev = reinterpret_cast<float*>((char*)k->fast_scratch + k->fast_image_bytes + 256);
+            axc::DoneSignal done{words, k->status_dev + 4, seq, (float*)sy.dev};   // sy.dev: the mapped host view
+            axc::HostX hx{(const float*)sx.staging_dev, words + 1, words + 2, seq};
+            axc::MatvecTuning tune = k->tune;
+            tune.x_prepared = k->fast_scratch;
+            tune.done = &done;
+            tune.host_x = &hx;
+            tune.pdl = 0;   // nothing is in flight before it: a plain launch
+            e = k->kind == KernelKind::Q4K
+                    ? axc::launch_q4k_matvec((const uint8_t*)sq.dev, nullptr, y_dev, (uint32_t)rows, n, k->status_dev, st, tune, k->sm_count, nullptr)
+                    : axc::launch_q4_0_matvec((const uint8_t*)sq.dev, nullptr, y_dev, (uint32_t)rows, n, k->status_dev, st, tune, k->sm_count, nullptr);
         } else {
             const axc::MatvecTuning& tune = k->tune;
             e = k->kind == KernelKind::Q4K

@@ -94,14 +94,58 @@ struct StreamParams {
     uint32_t* done_counter;
     uint32_t* done_flag;
     uint32_t done_seq;
+    float* y_host;           // with done_flag: y (device memory) is copied here by the last CTA
+    // PREPARED kernels, single-launch host dispatch: x lies in mapped HOST memory.  The first
+    // x_n_prod CTAs read it over PCIe and write the quantised image (x_prepared) before they turn
+    // to their rows; the last of them publishes x_seq in *x_ready, which every CTA waits for
+    // (bounded) before it reads the image.  Producers never wait for anyone and carry the lowest
+    // block indices, so they are running or finished whenever a later CTA is waiting.
+    const float* x_host;
+    uint32_t* x_ready;
+    uint32_t* x_prod_counter;
+    uint32_t x_seq;
+    uint32_t x_n_prod;
 };
 
-// One thread per CTA, after the CTA's stores of y (each storing thread has fenced, then a CTA-wide
-// barrier): count this CTA in; the last CTA of the grid resets the counter for the next launch
-// and publishes the sequence number where the host can see it.
-__device__ __forceinline__ void signal_cta_done(const StreamParams& p) {
-    __threadfence_system();
-    if (atomicAdd(p.done_counter, 1u) == gridDim.x - 1) {
+// Completion for a polling host, called by every thread of a CTA after the CTA's stores of y (to
+// device memory).  CTAs count themselves in at device scope (cheap); the last CTA of the grid
+// copies the whole of y to the host buffer, then ONE system-scope fence orders that copy before
+// the sequence number it publishes where the host polls.  (System-scope fences are expensive when
+// stores to host memory are outstanding and they serialise across the GPU: y stored to the host
+// by every CTA cost 16 us per launch with a fence per storing thread and 8 us with one per CTA;
+// this form costs about as much as the copy.)
+__device__ __forceinline__ void signal_cta_done(const StreamParams& p, uint32_t tid) {
+    __shared__ uint32_t s_last;
+    __syncthreads();   // every thread's stores of y are issued
+    if (tid == 0) {
+        __threadfence();
+        s_last = atomicAdd(p.done_counter, 1u) == gridDim.x - 1 ? 1u : 0u;
+    }
+    __syncthreads();
+    if (!s_last) return;
+    __threadfence();
+    if (p.y_host) {
+        const uint32_t n4 = p.rows >> 2;
+        const float4* src = reinterpret_cast<const float4*>(p.y);
+        float4* dst = reinterpret_cast<float4*>(p.y_host);
+        // loads in batches of eight before their stores: the loop is latency-bound otherwise
+        for (uint32_t base = 0; base < n4; base += 8u * blockDim.x) {
+            float4 v[8];
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+                const uint32_t i = base + u * blockDim.x + tid;
+                if (i < n4) v[u] = __ldcg(src + i);
+            }
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+                const uint32_t i = base + u * blockDim.x + tid;
+                if (i < n4) dst[i] = v[u];
+            }
+        }
+        for (uint32_t i = (n4 << 2) + tid; i < p.rows; i += blockDim.x) p.y_host[i] = __ldcg(p.y + i);
+        __syncthreads();
+    }
+    if (tid == 0) {
         *p.done_counter = 0;
         __threadfence_system();
         asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(p.done_flag), "r"(p.done_seq) : "memory");
@@ -442,7 +486,7 @@ __global__ void __launch_bounds__(512, 1) q4_matvec_stream_kernel(const StreamPa
     const uint32_t my_rows = p.rows_base + (bid < p.rows_rem ? 1u : 0u);
     const uint32_t r1 = r0 + my_rows;
     if (my_rows == 0) {
-        if (p.done_flag && tid == 0) signal_cta_done(p);
+        if (p.done_flag) signal_cta_done(p, tid);
         return;
     }
     const uint32_t n_tiles = bid < p.rows_rem ? p.tiles_hi : p.tiles_lo;
@@ -514,7 +558,60 @@ __global__ void __launch_bounds__(512, 1) q4_matvec_stream_kernel(const StreamPa
     if constexpr (PREPARED) {
         // The digit words were produced once by a prepare kernel; every thread reads its own
         // position's words straight into registers below (coalesced: consecutive lanes, consecutive
-        // 16-byte words), so there is nothing to stage and nothing to wait for here.
+        // 16-byte words), so there is nothing to stage and nothing to wait for here ...
+        if (p.x_host) {
+            // ... unless this launch carries its own producers (x in mapped host memory).
+            uint4* image = reinterpret_cast<uint4*>(const_cast<void*>(p.x_prepared));
+            if (bid < p.x_n_prod) {
+                // 64 positions (16 KB of x) at a time: fully coalesced 16-byte loads from host memory,
+                // all of a thread's loads issued together (one PCIe round trip), staged in shared
+                // memory, then quantised from there.
+                const float4* xh = reinterpret_cast<const float4*>(p.x_host);
+                float4* stage = reinterpret_cast<float4*>(smem + p.xs_offset);   // 1024 float4
+                const uint32_t n_f4 = p.n_pos * 16u;
+                for (uint32_t pos0 = bid * 64u; pos0 < p.x_pitch; pos0 += p.x_n_prod * 64u) {
+                    for (uint32_t base = 0; base < 1024u; base += 8u * blockDim.x) {   // one round for >= 128 threads
+                        float4 v[8];
+#pragma unroll
+                        for (int u = 0; u < 8; ++u) {
+                            const uint32_t idx = base + u * blockDim.x + tid, gi = pos0 * 16u + idx;
+                            v[u] = idx < 1024u && gi < n_f4 ? __ldg(xh + gi) : make_float4(0.f, 0.f, 0.f, 0.f);
+                        }
+#pragma unroll
+                        for (int u = 0; u < 8; ++u) {
+                            const uint32_t idx = base + u * blockDim.x + tid;
+                            if (idx < 1024u) stage[idx] = v[u];
+                        }
+                    }
+                    __syncthreads();
+                    (void)quantize_x_positions_from(
+                        [&](uint32_t i, float4* w) {
+#pragma unroll
+                            for (int u = 0; u < 4; ++u) w[u] = stage[i - pos0 * 16u + u];
+                        },
+                        image, reinterpret_cast<float4*>(image + 16u * p.x_pitch), p.n_pos, min(pos0 + 64u, p.x_pitch),
+                        p.x_pitch, tid, blockDim.x, pos0);
+                    __syncthreads();
+                }
+                __threadfence();
+                __syncthreads();
+                if (tid == 0 && atomicAdd(p.x_prod_counter, 1u) == p.x_n_prod - 1u) {
+                    *p.x_prod_counter = 0;
+                    __threadfence();
+                    asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(p.x_ready), "r"(p.x_seq) : "memory");
+                }
+            }
+            if (tid == 0) {
+                uint32_t it = 0, got = 0;
+                for (; it < (1u << 22); ++it) {
+                    asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(got) : "l"(p.x_ready) : "memory");
+                    if (got == p.x_seq) break;
+                    __nanosleep(20);
+                }
+                if (it == (1u << 22) && p.status) atomicOr(p.status, ERR_BULK_WAIT_TIMEOUT);
+            }
+            __syncthreads();
+        }
     } else if constexpr (XFUSE) {
         uint32_t x_epoch = 0;
         if (p.x_pairs || p.x2_pairs)
@@ -569,12 +666,14 @@ __global__ void __launch_bounds__(512, 1) q4_matvec_stream_kernel(const StreamPa
         const uint32_t pos = active ? my_pos : 0u;
         const uint4* xs_src = PREPARED ? reinterpret_cast<const uint4*>(p.x_prepared) : xs;
         const float4* xm_src = PREPARED ? reinterpret_cast<const float4*>(xs_src + 16u * p.x_pitch) : xm;
+        // a prepared image may have been written by CTAs of this very launch: read it through L2
 #pragma unroll
         for (int k = 0; k < 16; ++k) {
-            const uint4 a = xs_src[k * p.x_pitch + (pos ^ (uint32_t)(k & 7))];
+            const uint4* src = xs_src + k * p.x_pitch + (pos ^ (uint32_t)(k & 7));
+            const uint4 a = PREPARED ? __ldcg(src) : *src;
             ctx.dg[k][0] = a.x, ctx.dg[k][1] = a.y, ctx.dg[k][2] = a.z;
         }
-        const float4 meta = xm_src[pos];
+        const float4 meta = PREPARED ? __ldcg(xm_src + pos) : xm_src[pos];
         ctx.ps_a = meta.z, ctx.ps_b = meta.w;
         // sums of each digit over a group of columns: bytes dotted with ones (exact)
         auto digit_sums = [&](int k0, int nk, int (&out)[3]) {
@@ -714,11 +813,7 @@ __global__ void __launch_bounds__(512, 1) q4_matvec_stream_kernel(const StreamPa
             }
         }
     }
-    if (p.done_flag) {
-        __threadfence_system();   // this thread's stores of y, possibly to host memory
-        __syncthreads();
-        if (tid == 0) signal_cta_done(p);
-    }
+    if (p.done_flag) signal_cta_done(p, tid);
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -788,7 +883,8 @@ static cudaError_t launch_stream(const uint8_t* q, const float* x, float* y, uin
     const size_t smem_cap = (size_t)(227 * 1024) / resident - 1024;  // 1 KB per CTA is reserved
     p.x_pitch = (n_pos + 7) & ~7u;
     // digit words and per-position sums/scales; a prepared x is read straight into registers
-    const size_t xs_bytes = tune.x_prepared ? 0 : (size_t)16 * p.x_pitch * 16;
+    // (a launch that quantises x from host memory itself stages 16 KB of it at a time there)
+    const size_t xs_bytes = tune.x_prepared ? (tune.host_x ? (size_t)16384 : 0) : (size_t)16 * p.x_pitch * 16;
     const size_t xm_bytes = tune.x_prepared ? 0 : (size_t)p.x_pitch * 16;
     const size_t fixed = (((size_t)p.part_entries * 4 + 64 + 15) & ~(size_t)15) + xs_bytes + xm_bytes;
     int passes = 4;
@@ -833,10 +929,20 @@ static cudaError_t launch_stream(const uint8_t* q, const float* x, float* y, uin
     p.tiles_lo = (p.rows_base + p.tile_rows - 1) / p.tile_rows;
     p.tiles_hi = (p.rows_base + 1 + p.tile_rows - 1) / p.tile_rows;
     p.evict_first = tune.evict_first > 0 ? 1u : 0u;
-    p.prefetch_first = tune.pdl >= 2 || tune.pdl < 0 ? 1u : 0u;
+    p.prefetch_first = tune.pdl >= 2 || tune.pdl < 0 || tune.host_x ? 1u : 0u;
     // a prepared x is the output of the launch directly before: never read it ahead of the wait
     p.independent = tune.pdl == 3 && !tune.x_prepared ? 1u : 0u;
-    if (tune.done) p.done_counter = tune.done->counter, p.done_flag = tune.done->flag, p.done_seq = tune.done->seq;
+    if (tune.done) {
+        p.done_counter = tune.done->counter, p.done_flag = tune.done->flag, p.done_seq = tune.done->seq;
+        p.y_host = tune.done->y_host;
+    }
+    if (tune.host_x) {
+        if (!tune.x_prepared) return cudaErrorInvalidValue;
+        p.x_host = tune.host_x->x_host, p.x_ready = tune.host_x->ready, p.x_prod_counter = tune.host_x->counter;
+        p.x_seq = tune.host_x->seq;
+        p.x_n_prod = (p.x_pitch + 63u) / 64u;
+        if (p.x_n_prod > grid) p.x_n_prod = grid;
+    }
 
     void (*kern)(StreamParams) = nullptr;
     if (tune.gather) {

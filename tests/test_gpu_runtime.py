@@ -11,6 +11,8 @@ import time
 import numpy as np
 import pytest
 
+torch = pytest.importorskip("torch")
+
 import oracle
 
 pytestmark = pytest.mark.gpu
@@ -271,4 +273,37 @@ def test_bound_dispatch_repeats_and_rereads_host_input(axc, ctx, synth):
     out2 = f32(b.run()[2])
     assert np.array_equal(out2, 2.0 * out1)     # scaling x by two is exact in every step of the kernel
     assert b.run() is b.outputs
+    h.drop()
+
+
+@pytest.mark.parametrize("entry,rows,n", [
+    ("q4km_dequant_matvec", 14336, 16),    # one producer CTA for x
+    ("q4km_dequant_matvec", 4096, 56),     # K = 14336: four producer CTAs
+    ("q4km_dequant_matvec", 300, 128),     # K = 32768: eight
+    ("q4km_dequant_matvec", 64, 1),
+    ("q4_0_dequant_matvec", 4096, 128),
+    ("q4km_dequant_matvec", 63, 16),       # below the row limit of the single-launch path: copy path
+])
+def test_single_launch_dispatch_matches_the_resident_path(axc, ctx, ops, synth, entry, rows, n):
+    """dispatch_handle with resident weights and a fresh host x per call takes the single-launch
+    path (x read from mapped host memory by the kernel's first CTAs, y copied to the host by its
+    last CTA, completion polled): bit-identical to the device-resident call on the same inputs,
+    call after call (a stale x image or an early completion flag would show), and to the timed
+    (copy-and-event) path."""
+    q4k = entry == "q4km_dequant_matvec"
+    q = (synth.q4k_weights if q4k else synth.q4_0_weights)(rows, n, 8800 + rows + n)
+    k = n * (256 if q4k else 32)
+    plan = axc.q4_matvec_binding_plan(entry)
+    h = ctx.prepare_kernel(SPIRV_STANDIN, plan, 4, entry, spirv_hash=0x5F00 + rows + n)
+    x0 = synth.activations(k, 1)
+    ctx.dispatch_handle(h, (rows, 1, 1), [q, x0, b""], [0, 0, rows * 4], pc(n))      # weights uploaded once
+    qd = torch.from_numpy(q).cuda()
+    fn = ops.q4k_matvec if q4k else ops.q4_0_matvec
+    for it in range(12):
+        x = synth.activations(k, 8900 + it) * np.float32(1.5 ** it)
+        out = ctx.dispatch_handle(h, (rows, 1, 1), [b"", x, b""], [0, 0, rows * 4], pc(n))
+        want = fn(qd, torch.from_numpy(x).cuda(), rows, n).cpu().numpy()
+        assert np.array_equal(f32(out[2]), want), it
+    out_t, st = ctx.dispatch_handle(h, (rows, 1, 1), [b"", b"", b""], [0, 0, rows * 4], pc(n), stats=True)
+    assert np.array_equal(f32(out_t[2]), want) and st.rows_effective == rows      # resident x, copy path
     h.drop()
