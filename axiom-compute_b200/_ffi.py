@@ -136,6 +136,8 @@ SYMBOLS = {
     "axc_cuda_gather_next_epoch": (C.c_int, [_VP, _VP]),
     "axc_cuda_gather_finish": (C.c_int, [_VP, _VP, _VP, C.c_uint32, _VP, _VP, C.c_uint32, C.c_uint64,
                                          C.POINTER(AxcGatherSync)]),
+    "axc_cuda_gather_reduce_finish": (C.c_int, [_VP, _VP, _VP, C.c_uint32, C.c_uint32, C.c_uint64, _VP, _VP, C.c_uint32,
+                                                C.c_uint64]),
     "axc_cuda_q4k_matvec_static": (C.c_int, [_VP, _VP, _VP, C.c_uint32, C.c_uint32, _VP]),
     "axc_cuda_q4k_matvec_static_warmup": (C.c_int, []),
     "axc_cuda_version": (C.c_int, []),

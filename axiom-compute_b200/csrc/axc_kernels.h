@@ -110,6 +110,10 @@ cudaError_t launch_gather_finish(const uint64_t* pairs, const uint32_t* epoch_pt
                                  uint32_t* status, cudaStream_t stream, bool overlap, uint64_t parity_stride = 0,
                                  const GatherSync* sync = nullptr);
 cudaError_t launch_gather_next_epoch(uint32_t* epoch_ptr, cudaStream_t stream);
+// out[i] = sum over parts r < n_parts of the value of word pairs[r * part_stride / 8 + i] (K-sharded linears).
+cudaError_t launch_gather_reduce_finish(const uint64_t* pairs, const uint32_t* epoch_ptr, float* out, uint32_t n,
+                                        uint32_t n_parts, uint64_t part_stride, uint32_t* status, cudaStream_t stream,
+                                        bool overlap, uint64_t parity_stride);
 
 // Quantised form of x for `n_pos` 64-column positions (see q4_stream.cu): bytes needed and the
 // kernel that fills them; a matvec launched with tuning.x_prepared set reads it instead of x.

@@ -1060,6 +1060,19 @@ int axc_cuda_gather_finish(const uint64_t* pairs, const uint32_t* epoch, float* 
                                                    sync ? &gs : nullptr));
 }
 
+int axc_cuda_gather_reduce_finish(const uint64_t* pairs, const uint32_t* epoch, float* out, uint32_t n,
+                                  uint32_t n_parts, uint64_t part_stride_bytes, void* stream, uint32_t* status,
+                                  uint32_t flags, uint64_t parity_stride_bytes) {
+    clear_error();
+    if (n == 0) return AXC_OK;
+    if (!pairs || !epoch || !out || ((uintptr_t)pairs & 7u) || ((part_stride_bytes | parity_stride_bytes) & 7u))
+        return fail(AXC_ERR_INVALID_ARGUMENT, "null or misaligned pair storage / epoch / output");
+    if (n_parts == 0 || n_parts > 16) return fail(AXC_ERR_INVALID_ARGUMENT, "1..16 parts");
+    return launch_result(axc::launch_gather_reduce_finish(pairs, epoch, out, n, n_parts, part_stride_bytes, status,
+                                                          (cudaStream_t)stream, (flags & AXC_FINISH_OVERLAP_PREVIOUS) != 0,
+                                                          parity_stride_bytes));
+}
+
 int axc_cuda_q4k_matvec_plan(uint32_t rows, uint32_t n_superblocks, const axc_tuning* tuning,
                              int32_t sm_count, int32_t out[5]) {
     clear_error();

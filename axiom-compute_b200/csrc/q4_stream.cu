@@ -1091,6 +1091,76 @@ __global__ void gather_finish_kernel(const uint64_t* __restrict__ pairs, const u
 
 __global__ void gather_next_epoch_kernel(uint32_t* epoch_ptr) { *epoch_ptr += 1; }
 
+// Consumer side of a K-sharded linear: every rank stored its full-length vector of PARTIAL sums
+// into its own part of the (value, epoch) storage of every rank (the all-gather epilogue with
+// row offset 0 and one part per rank); this kernel waits (bounded, as gather_finish_kernel) for
+// all `n_parts` words of each element and writes their sum, taken in part order on every rank
+// (so all ranks obtain bit-identical vectors), as a plain fp32 vector.
+__global__ void gather_reduce_finish_kernel(const uint64_t* __restrict__ pairs, const uint32_t* __restrict__ epoch_ptr,
+                                            float* __restrict__ out, uint32_t n, uint32_t n_parts, uint64_t part_stride,
+                                            uint32_t* status, uint32_t overlap, uint64_t parity_stride) {
+    if (!overlap) asm volatile("griddepcontrol.wait;" ::: "memory");
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    uint32_t epoch;
+    asm volatile("ld.relaxed.gpu.global.u32 %0, [%1];" : "=r"(epoch) : "l"(epoch_ptr) : "memory");
+    pairs += (size_t)(epoch & 1u) * (parity_stride >> 3);
+    const size_t stride_w = part_stride >> 3;
+    bool gave_up = false, ahead = false;
+    for (uint32_t i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) {
+        float sum = 0.0f;
+        uint32_t pending = n_parts >= 32u ? 0xFFFFFFFFu : (1u << n_parts) - 1u;
+        float part[16];
+        uint32_t it = gave_up ? (1u << 22) - 1u : 0u;
+        for (; pending && it < (1u << 22); ++it) {
+#pragma unroll
+            for (uint32_t r = 0; r < 16u; ++r) {
+                if (r < n_parts && (pending >> r & 1u)) {
+                    uint64_t w;
+                    asm volatile("ld.relaxed.sys.global.b64 %0, [%1];" : "=l"(w) : "l"(pairs + r * stride_w + i) : "memory");
+                    const int32_t d = (int32_t)((uint32_t)(w >> 32) - epoch);
+                    if (d >= 0) {
+                        part[r] = __uint_as_float((uint32_t)w);
+                        pending &= ~(1u << r);
+                        ahead = ahead || d > 0;
+                    }
+                }
+            }
+            if (pending) __nanosleep(100);
+        }
+        if (pending) {
+            gave_up = true;
+#pragma unroll
+            for (uint32_t r = 0; r < 16u; ++r)
+                if (pending >> r & 1u) part[r] = 0.0f;
+        }
+#pragma unroll
+        for (uint32_t r = 0; r < 16u; ++r)
+            if (r < n_parts) sum += part[r];
+        out[i] = sum;
+    }
+    if (status) {
+        if (gave_up) atomicOr(status, ERR_PEER_WAIT_TIMEOUT);
+        if (ahead) atomicOr(status, ERR_EPOCH_AHEAD);
+    }
+}
+
+cudaError_t launch_gather_reduce_finish(const uint64_t* pairs, const uint32_t* epoch_ptr, float* out, uint32_t n,
+                                        uint32_t n_parts, uint64_t part_stride, uint32_t* status, cudaStream_t stream,
+                                        bool overlap, uint64_t parity_stride) {
+    if (n == 0) return cudaSuccess;
+    if (n_parts == 0 || n_parts > 16) return cudaErrorInvalidValue;
+    uint32_t blocks = (n + 127) / 128;
+    if (blocks > 592) blocks = 592;
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(blocks), cfg.blockDim = dim3(128), cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr, cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, gather_reduce_finish_kernel, pairs, epoch_ptr, out, n, n_parts, part_stride, status,
+                              overlap ? 1u : 0u, parity_stride);
+}
+
 cudaError_t launch_gather_finish(const uint64_t* pairs, const uint32_t* epoch_ptr, float* out, uint32_t n,
                                  uint32_t* status, cudaStream_t stream, bool overlap, uint64_t parity_stride,
                                  const GatherSync* gs) {

@@ -27,6 +27,16 @@ next linear's input is the ``mode``:
   5.73 ms/token on two GPUs).
 * ``"poll"``: as "fused", but every consumer CTA polls the (value, epoch) words itself (no launch in
   between, 2 x the bytes per CTA past L1: measured slower).
+* ``"paired"`` (several GPUs only): the linears are sharded in pairs so that a layer has two exchanges
+  instead of four.  qkv and gate+up are sharded by ROWS, each rank owning matching slices (its
+  rows of q, k and v; its rows of g and of u); o and down are sharded by COLUMNS: a rank multiplies
+  its column range of Wo with its own slice of q (of Wdown with its own g + u), which it has
+  locally, and stores the full-length vector of partial sums into every rank's storage; a
+  reduce-finish kernel sums the parts (same order on every rank) into the plain vector the next
+  row-sharded linear stages.  The unit-RMS scale of q and of g + u never has to be exchanged:
+  both feed a linear whose output is normalised again before use, and unitRMS(s v) = unitRMS(v).
+  The sums of partial products are rounded differently from the one-GPU order, within the same
+  bar; the vectors o and d held here are the unscaled sums.
 
 Weights are synthetic (uniform nibbles and scale bytes, d and dmin = f16(|N(0,1)| * 0.01)),
 generated on the device in eight row chunks per linear so that the global matrices are the same
@@ -93,7 +103,7 @@ def full_matrix(shape: SweepShape, seed: int, layer: int, j: int, device) -> tor
                       for c in range(CHUNKS)])
 
 
-MODES = ("prepared", "fused", "poll", "mixed")
+MODES = ("prepared", "fused", "poll", "mixed", "paired")
 
 
 class DecodeSweep:
@@ -125,6 +135,9 @@ class DecodeSweep:
         for _n, rows, k in shape.linears:
             if rows % CHUNKS or k % 256 or k // 256 > 128:
                 raise ValueError("every linear needs rows divisible by 8 and K a multiple of 256 up to 32768")
+        if self.mode == "paired":
+            self._init_paired(shape, seed, group)
+            return
         per = CHUNKS // self.world
         # weights[layer][j]: this rank's contiguous rows of linear j
         self.weights: List[List[torch.Tensor]] = []
@@ -262,6 +275,8 @@ class DecodeSweep:
         how the previous token's d becomes this token's h), leaves the last layer's d in
         ``self.d_last`` and every linear's output in the vector store."""
         sh = self.shape
+        if self.mode == "paired":
+            return self._token_paired(normalise_input)
         with torch.cuda.device(self.device):
             if self.world > 1:
                 _raise_for(_ffi.lib().axc_cuda_gather_next_epoch(self.epoch.data_ptr(), self._stream()))
@@ -292,6 +307,118 @@ class DecodeSweep:
                     self.parity_stride, None))
             self.d_last.copy_(self.vec[last:last + sh.hidden])
 
+    # -- paired sharding (rows for qkv and gate+up, columns for o and down) -------------------
+    def _init_paired(self, shape: SweepShape, seed: int, group) -> None:
+        import torch.distributed as dist
+        import torch.distributed._symmetric_memory as symm_mem
+        W, r, dev = self.world, self.rank, self.device
+        if W < 2:
+            raise ValueError("mode 'paired' needs more than one rank")
+        hid, kv, ffn = shape.hidden, shape.kv, shape.ffn
+        if hid % (256 * W) or ffn % (256 * W) or kv % W:
+            raise ValueError("paired sharding needs hidden and ffn divisible by 256 * world and kv by world")
+        hq, hk, hf = hid // W, kv // W, ffn // W
+        self.slices = (hq, hk, hf)
+        self.parallelism = (f"qkv and gate+up sharded by rows, o and down by columns over {W} GPUs: two exchanges "
+                            "per layer (partial sums stored into every rank by the producer's epilogue, summed by a "
+                            "reduce-finish kernel)")
+        self.weights = []
+        for layer in range(shape.layers):
+            row = []
+            for j, (_n, rows, k) in enumerate(shape.linears):
+                n_sb = k // 256
+                full = full_matrix(shape, seed, layer, j, dev).view(rows, n_sb, 144)
+                if j == 0:      # this rank's rows of q, of k and of v
+                    part = torch.cat([full[r * hq:(r + 1) * hq], full[hid + r * hk:hid + (r + 1) * hk],
+                                      full[hid + kv + r * hk:hid + kv + (r + 1) * hk]])
+                elif j == 2:    # this rank's rows of g and of u
+                    part = torch.cat([full[r * hf:(r + 1) * hf], full[ffn + r * hf:ffn + (r + 1) * hf]])
+                else:           # this rank's columns (whole superblocks) of every row
+                    per = n_sb // W
+                    part = full[:, r * per:(r + 1) * per]
+                row.append(part.contiguous().view(-1))
+                del full, part
+            self.weights.append(row)
+        L = shape.layers
+        # (value, epoch) storage: per layer W parts of o partial sums and W parts of d partial sums, two copies
+        self._words_layer = 2 * W * hid
+        words = self._words_layer * L
+        self.pairs = symm_mem.empty(2 * words, dtype=torch.int64, device=dev)
+        self.pairs.zero_()
+        self._handle = symm_mem.rendezvous(self.pairs, group if group is not None else dist.group.WORLD)
+        ptrs = list(self._handle.buffer_ptrs)
+        torch.cuda.synchronize(dev)
+        dist.barrier(group)
+        self.ptr_table = torch.tensor(ptrs, dtype=torch.int64, device=dev)
+        self.parity_stride = words * 8
+        # plain local vectors, per layer: [q k v slices | o sum | g u slices | d sum]
+        self._loc = (hq + 2 * hk, hid, 2 * hf, hid)
+        self._loc_off = [0, self._loc[0], self._loc[0] + hid, self._loc[0] + hid + 2 * hf]
+        self._loc_layer = sum(self._loc)
+        self.vec = torch.zeros(self._loc_layer * L, dtype=torch.float32, device=dev)
+        self.status = torch.zeros(1, dtype=torch.int32, device=dev)
+        self.epoch = torch.zeros(1, dtype=torch.int32, device=dev)
+        self.h = torch.zeros(hid, dtype=torch.float32, device=dev)
+        self.d_last = torch.zeros(hid, dtype=torch.float32, device=dev)
+        self.checkable_outputs = ()        # full q/k/v and g/u exist nowhere; o and d are unscaled sums
+        self.prepared_linear = [False] * 4
+        self.finish_after = [False, True, False, True]
+        self.launches_per_token = 6 * L + 2
+        self._group = group
+
+    def _vec_ptr(self, layer: int, part: int, off: int = 0) -> int:
+        return self.vec.data_ptr() + (layer * self._loc_layer + self._loc_off[part] + off) * 4
+
+    def _token_paired(self, normalise_input: bool) -> None:
+        sh, W, r = self.shape, self.world, self.rank
+        hq, hk, hf = self.slices
+        hid = sh.hidden
+        L = _ffi.lib()
+        st = self.status.data_ptr()
+        tn = C.byref(self.tuning) if self.tuning is not None else None
+        ep = self.epoch.data_ptr()
+        stream = self._stream
+        with torch.cuda.device(self.device):
+            _raise_for(L.axc_cuda_gather_next_epoch(ep, stream()))
+            for layer in range(sh.layers):
+                wq, wo, wgu, wd = self.weights[layer]
+                base = layer * self._words_layer          # word offset of this layer's parts
+                # qkv (rows): x = h (first layer) or the summed d of the layer before, unit RMS
+                if layer == 0:
+                    x = _ffi.AxcXSrc(self.h.data_ptr(), None, None, None, None, 1 if normalise_input else 0, 0)
+                else:
+                    x = _ffi.AxcXSrc(self._vec_ptr(layer - 1, 3), None, None, None, None, 1, 0)
+                _raise_for(L.axc_cuda_q4k_matvec_fused(wq.data_ptr(), C.byref(x), self._vec_ptr(layer, 0), hq + 2 * hk,
+                                                       hid // 256, None, stream(), st, tn))
+                # o (columns): this rank's slice of q times its columns of Wo -> part `rank` on every rank
+                x = _ffi.AxcXSrc(self._vec_ptr(layer, 0), None, None, None, None, 0, 0)
+                g = _ffi.AxcGather(self.ptr_table.data_ptr(), (base + r * hid) * 8, ep, W, r, 0, self.parity_stride)
+                _raise_for(L.axc_cuda_q4k_matvec_fused(wo.data_ptr(), C.byref(x), None, hid, hq // 256, C.byref(g),
+                                                       stream(), st, tn))
+                _raise_for(L.axc_cuda_gather_reduce_finish(self.pairs.data_ptr() + base * 8, ep, self._vec_ptr(layer, 1), hid,
+                                                           W, hid * 8, stream(), st, _ffi.AXC_FINISH_OVERLAP_PREVIOUS,
+                                                           self.parity_stride))
+                # gate+up (rows): x = summed o, unit RMS
+                x = _ffi.AxcXSrc(self._vec_ptr(layer, 1), None, None, None, None, 1, 0)
+                _raise_for(L.axc_cuda_q4k_matvec_fused(wgu.data_ptr(), C.byref(x), self._vec_ptr(layer, 2), 2 * hf,
+                                                       hid // 256, None, stream(), st, tn))
+                # down (columns): (g + u) slice times this rank's columns of Wdown -> parts of d
+                x = _ffi.AxcXSrc(self._vec_ptr(layer, 2), self._vec_ptr(layer, 2, hf), None, None, None, 0, 0)
+                g = _ffi.AxcGather(self.ptr_table.data_ptr(), (base + (W + r) * hid) * 8, ep, W, r, 0, self.parity_stride)
+                _raise_for(L.axc_cuda_q4k_matvec_fused(wd.data_ptr(), C.byref(x), None, hid, hf // 256, C.byref(g),
+                                                       stream(), st, tn))
+                _raise_for(L.axc_cuda_gather_reduce_finish(self.pairs.data_ptr() + (base + W * hid) * 8, ep,
+                                                           self._vec_ptr(layer, 3), hid, W, hid * 8, stream(), st,
+                                                           _ffi.AXC_FINISH_OVERLAP_PREVIOUS, self.parity_stride))
+            last = (sh.layers - 1) * self._loc_layer + self._loc_off[3]
+            self.d_last.copy_(self.vec[last:last + hid])
+
+    def local_output(self, layer: int, part: int) -> torch.Tensor:
+        """paired mode: this rank's plain vectors of `layer`: 0 = its slices of q, k, v; 1 = the summed o;
+        2 = its slices of g, u; 3 = the summed d (o and d without the unit-RMS scale of their input)."""
+        o = layer * self._loc_layer + self._loc_off[part]
+        return self.vec[o:o + self._loc[part]]
+
     def _plain_store(self) -> torch.Tensor:
         return self.vec
 
@@ -308,6 +435,12 @@ class DecodeSweep:
     def kv_checksum(self) -> torch.Tensor:
         """Sum of every layer's k and v entries (fp64, on the device)."""
         sh = self.shape
+        if self.mode == "paired":      # every rank holds its slices of k and v: sum them over the ranks
+            import torch.distributed as dist
+            hq, hk, _hf = self.slices
+            v = self.vec.view(sh.layers, self._loc_layer)[:, hq:hq + 2 * hk].double().sum()
+            dist.all_reduce(v, group=self._group)
+            return v
         per = sh.vector_words_per_layer
         v = self._plain_store().view(sh.layers, per)[:, sh.hidden:sh.hidden + 2 * sh.kv]
         return v.double().sum()

@@ -248,9 +248,11 @@ class BenchVariantResponse:
     device_median_ns: int = 0
     device_samples: List[int] = field(default_factory=list)
     workgroups: List[int] = field(default_factory=list)
+    output_bytes: Optional[bytes] = None    # y of the last sample (for policies that compare variants); not serialised
 
     def to_json_obj(self):
         d = asdict(self)
+        d.pop("output_bytes", None)
         d["correctness"] = self.correctness.to_json_obj()
         return d
 
@@ -336,9 +338,10 @@ def bench_variant(req: BenchVariantRequest, ctx: McpContext) -> BenchVariantResp
         correctness = check_against_strict(cuda, meta, workgroups, inputs, output_sizes, pc, outputs)
     finally:
         handle.drop()
+    y_bytes = bytes(outputs[2]) if outputs is not None and len(outputs) > 2 else None
     return BenchVariantResponse(median_ns, samples, correctness,
                                 build_machine_metadata(cuda, ctx.git_sha),
-                                _median(dev_ns) if dev_ns else 0, dev_ns, workgroups)
+                                _median(dev_ns) if dev_ns else 0, dev_ns, workgroups, y_bytes)
 
 
 # ------------------------------------------------------------------ grid search (axc-optimize)
@@ -355,10 +358,9 @@ class CorrectnessPolicy:
         if text == "bit-exact":
             return CorrectnessPolicy("BitExact")
         if text.startswith("fp-tol:"):
-            try:
-                return CorrectnessPolicy("EquivFpTol", int(text[7:]))
-            except ValueError:
-                return CorrectnessPolicy("None")
+            digits = text[7:]
+            ok = digits.isascii() and digits.isdigit() and int(digits) <= 0xFFFFFFFF
+            return CorrectnessPolicy("EquivFpTol", int(digits) if ok else 4)   # an unparsable count means 4
         return CorrectnessPolicy("None")
 
 
@@ -506,6 +508,28 @@ def append_history_entry(path: str, entry: dict) -> None:
         f.flush()
 
 
+def policy_failure(policy: CorrectnessPolicy, got: Optional[bytes], ref: Optional[bytes]) -> Optional[tuple]:
+    """The policy applied to a variant's output bytes against those of the ordinal-0 variant, as
+    the reference does (grid_search.rs:54-75): ``BitExact`` rejects any differing element with
+    ``("BitMismatch", count)``; ``EquivFpTol{ulp}`` rejects elements further than `ulp` units in the
+    last place with ``("UlpExceeded", count, max_ulp)``.  None = accepted."""
+    if policy.kind == "None":
+        return None
+    if got is None or ref is None:
+        return ("OracleError", "no output to compare")
+    if len(got) != len(ref):
+        return ("OracleError", f"output length {len(got)} != reference length {len(ref)}")
+    a = np.frombuffer(got[:len(got) // 4 * 4], dtype=np.float32)
+    b = np.frombuffer(ref[:len(ref) // 4 * 4], dtype=np.float32)
+    if policy.kind == "BitExact":
+        count = int((a.view(np.uint32) != b.view(np.uint32)).sum())
+        return ("BitMismatch", count) if count else None
+    d = ulp_distance(a, b)
+    d = np.where(np.isnan(a) | np.isnan(b), np.where(a.view(np.uint32) == b.view(np.uint32), 0, 1 << 31), d)
+    count = int((d > policy.ulp).sum())
+    return ("UlpExceeded", count, int(min(int(d.max()), 0xFFFFFFFF))) if count else None
+
+
 def grid_search_tool(req: GridSearchRequest, ctx: McpContext) -> GridSearchResponse:
     """Every variant = one ``bench_variant`` with its assignments; ranked by wall-clock median
     like the reference (device medians are reported beside them)."""
@@ -526,11 +550,14 @@ def grid_search_tool(req: GridSearchRequest, ctx: McpContext) -> GridSearchRespo
         r = run(assignments)
         return SampleStats(r.median_ns, min(r.samples), max(r.samples), len(r.samples))
 
+    first = enumerate_strategy(dict(req.holes))[0].assignments if req.holes else {}
+
     def correctness_fn(assignments):
         r = run(assignments)
-        if r.correctness.kind == "Failed":
+        if r.correctness.kind == "Failed":     # wrong against the reference-order kernel: never a winner
             return ("OracleError", r.correctness.reason)
-        return None
+        # the stated policy: this variant's output against the ordinal-0 variant's
+        return policy_failure(policy, r.output_bytes, run(first).output_bytes)
 
     result = grid_search(dict(req.holes), policy, correctness_fn, bench_fn)
     ranked = []

@@ -878,9 +878,27 @@ def run_decode(args):
     rs, n_sb = 32, shape.hidden // 256
     rows0 = shape.linears[0][1]
     h0 = sweep.h.cpu().numpy()
-    got_all = sweep.output(0, 0).cpu().numpy()
     worst = 0.0
-    for c in range(decode.CHUNKS):
+    if sweep.mode == "paired":
+        # the first exchanged vector: o before its input's scale = sum over ranks of (columns of Wo) x (slice of q).
+        # q on the CPU from the whole first matrix, then sampled rows of Wo against it: a wrong or missing
+        # part of ANY rank shows in every row.
+        hid = shape.hidden
+        wq_full = decode.full_matrix(shape, sweep.seed, 0, 0, dev)[:hid * n_sb * 144].cpu().numpy()
+        q_full = oracle.matvec_rows("q4k", wq_full, h0, hid, n_sb)
+        wo_full = decode.full_matrix(shape, sweep.seed, 0, 1, dev).view(hid, -1)
+        got_o = sweep.local_output(0, 1).cpu().numpy()
+        for b in (0, hid // 2, hid - rs):
+            wo = wo_full[b:b + rs].contiguous().view(-1).cpu().numpy()
+            y_ref = oracle.matvec_rows("q4k", wo, q_full, rs, n_sb)
+            _y64, mag = oracle.matvec_rows_f64("q4k", wo, q_full, rs, n_sb)
+            err = float((np.abs(got_o[b:b + rs] - y_ref) / mag).max())
+            worst = max(worst, err)
+            if not err <= 2e-5:
+                raise SystemExit(f"rank {rank}: parity check failed before timing: summed o, rows {b}..: {err:.3e}")
+        del wo_full
+    got_all = sweep.output(0, 0).cpu().numpy() if sweep.mode != "paired" else None
+    for c in range(decode.CHUNKS if sweep.mode != "paired" else 0):
         wq = decode.synth_chunk(rows0 // decode.CHUNKS, n_sb, sweep.seed + c, dev)[:rs * n_sb * 144].cpu().numpy()
         y_ref = oracle.matvec_rows("q4k", wq, h0, rs, n_sb)
         _y64, mag = oracle.matvec_rows_f64("q4k", wq, h0, rs, n_sb)
@@ -942,8 +960,9 @@ def run_decode(args):
                    "parallelism": "single GPU" if world == 1 else sweep.parallelism},
         "aggregate_gbs": round(agg, 1), "kv_checksum": float(sweep.kv_checksum().item()),
         "us_per_layer": round(ms_tok * 1e3 / shape.layers, 2),
-        "peer_slice_check": {"row_chunks_checked": decode.CHUNKS, "rows_per_chunk": rs,
-                             "max_normwise_err": float(f"{worst:.3e}"), "gate": 1e-5},
+        "peer_slice_check": {"what": "summed partial products of every rank (o of layer 0), 3 x 32 rows" if sweep.mode == "paired"
+                             else f"first linear, {rs} rows of each of the {decode.CHUNKS} row chunks (every rank's slice)",
+                             "max_normwise_err": float(f"{worst:.3e}"), "gate": 2e-5 if sweep.mode == "paired" else 1e-5},
         "roofline": {"bound": "hbm", "achieved": round(agg / world, 1), "peak": peaks["hbm"], "unit": "GB/s",
                      "frac": round(agg / world / peaks["hbm"], 4), "traffic": None, "peak_source": peaks["hbm_src"],
                      "note": "per-GPU weight bytes per token / token time (all launches, gaps and exchanges included)"},

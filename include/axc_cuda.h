@@ -359,6 +359,18 @@ int axc_cuda_gather_finish(const uint64_t* pairs, const uint32_t* epoch, float* 
                            void* stream, uint32_t* status, uint32_t flags, uint64_t parity_stride_bytes,
                            const axc_gather_sync* sync);
 
+/* Consumer side of a linear sharded by COLUMNS (K) instead of rows: rank r multiplies its column
+ * range of every row with its slice of x and stores the full-length vector of partial sums into
+ * part r of every rank's pair storage (axc_cuda_q4k_matvec_fused with an axc_gather whose
+ * row_offset is 0 and whose y_offset_bytes selects part r: parts lie part_stride_bytes apart).
+ * This call waits (bounded, as axc_cuda_gather_finish) until all n_parts words of each of the n
+ * elements carry the current epoch and writes their sum, taken in part order on every rank so
+ * that all ranks obtain the same bits, to out as plain fp32.  flags and parity_stride_bytes as for
+ * axc_cuda_gather_finish.  No counterpart in the reference. */
+int axc_cuda_gather_reduce_finish(const uint64_t* pairs, const uint32_t* epoch, float* out, uint32_t n,
+                                  uint32_t n_parts, uint64_t part_stride_bytes, void* stream, uint32_t* status,
+                                  uint32_t flags, uint64_t parity_stride_bytes);
+
 /* Launch geometry the matvec launchers would use (no launch). */
 int axc_cuda_q4k_matvec_plan(uint32_t rows, uint32_t n_superblocks, const axc_tuning* tuning,
                              int32_t sm_count, int32_t out_grid_block_smem_tile_stages[5]);

@@ -11,14 +11,18 @@
 //   DispatchError (25 variants) / CopyDirection   crates/axc-runtime/src/error.rs:14-198
 //   ParamBindingPlan and its slots            crates/axc-hir/src/param.rs:66-126
 //   probe_vulkan_available, gpu_tests_enabled, captured_icd_path   crates/axc-runtime/src/icd.rs:22-80
+//   KernelMetadata, load_kernel_metadata, CURRENT_SCHEMA_VERSION   crates/axc-runtime/src/metadata.rs:35,45-122
 //
 // Rust's `Result<T, DispatchError>` becomes `axc::Result<T>` (a value or an error, never an
 // exception).  Header-only; link with libaxc_cuda.so.  There is no CPU fallback behind it.
 #pragma once
 
 #include <cstdint>
+#include <cstdio>
 #include <cstdlib>
 #include <cstring>
+#include <map>
+#include <memory>
 #include <optional>
 #include <string>
 #include <utility>
@@ -313,6 +317,231 @@ private:
 };
 using CudaContext = VulkanContext;
 using CudaContextOptions = VulkanContextOptions;
+
+// ---- metadata sidecar (crates/axc-runtime/src/metadata.rs) ----
+// `<output>.axc.meta.json`, schema v1: {schema_version, kernel_name, workgroup_size[3], binding_plan
+// {buffers[{name, ty{elem, access}, position, buffer_position}], scalars[{name, ty, offset,
+// member_index, position}], push_constant_total_bytes}, push_constant_total_bytes, entry_point};
+// enums are serde's external tags ("U8", "F32", "U32", "ReadOnly", ...); source spans are not
+// serialised.  load_kernel_metadata reads, parses, then checks the version, in the reference's
+// order: MetadataIoError, MetadataParseError, MetadataSchemaMismatch{got, supported} (carried in
+// `expected` = supported and `provided` = got).
+constexpr uint32_t CURRENT_SCHEMA_VERSION = 1;   // metadata.rs:35
+
+struct KernelMetadata {   // metadata.rs:45-71
+    uint32_t schema_version = CURRENT_SCHEMA_VERSION;
+    std::string kernel_name;
+    uint32_t workgroup_size[3] = {1, 1, 1};
+    ParamBindingPlan binding_plan;
+    uint32_t push_constant_total_bytes = 0;
+    std::string entry_point;
+    // metadata.rs:77-92: the version is the current one, the push-constant size the plan's
+    static KernelMetadata new_(std::string kernel_name, const uint32_t (&wg)[3], ParamBindingPlan plan,
+                               std::string entry_point) {
+        KernelMetadata m;
+        m.kernel_name = std::move(kernel_name), m.entry_point = std::move(entry_point);
+        for (int i = 0; i < 3; ++i) m.workgroup_size[i] = wg[i];
+        m.push_constant_total_bytes = plan.push_constant_total_bytes;
+        m.binding_plan = std::move(plan);
+        return m;
+    }
+};
+
+namespace detail {
+// A JSON value: just enough of a reader for the sidecar (objects, arrays, strings, numbers,
+// true / false / null; \uXXXX escapes below 0x80 only, which is all serde_json emits for ASCII names).
+struct Json {
+    enum Kind { Null, Bool, Num, Str, Arr, Obj } kind = Null;
+    bool b = false;
+    double num = 0;
+    std::string str;
+    std::vector<Json> arr;
+    std::vector<std::pair<std::string, Json>> obj;
+    const Json* get(const char* key) const {
+        for (const auto& kv : obj) if (kv.first == key) return &kv.second;
+        return nullptr;
+    }
+};
+struct JsonReader {
+    const char* p;
+    const char* end;
+    std::string err;
+    void ws() { while (p < end && (*p == ' ' || *p == '\n' || *p == '\r' || *p == '\t')) ++p; }
+    bool fail(const char* what) { if (err.empty()) err = what; return false; }
+    bool string(std::string& out) {
+        if (p >= end || *p != '"') return fail("expected a string");
+        ++p;
+        while (p < end && *p != '"') {
+            char c = *p++;
+            if (c == '\\') {
+                if (p >= end) return fail("unterminated escape");
+                const char e = *p++;
+                switch (e) {
+                    case 'n': c = '\n'; break; case 't': c = '\t'; break; case 'r': c = '\r'; break;
+                    case 'b': c = '\b'; break; case 'f': c = '\f'; break;
+                    case '"': case '\\': case '/': c = e; break;
+                    case 'u': {
+                        if (end - p < 4) return fail("short \\u escape");
+                        const unsigned v = (unsigned)std::strtoul(std::string(p, p + 4).c_str(), nullptr, 16);
+                        p += 4;
+                        if (v >= 0x80) return fail("non-ASCII \\u escape");
+                        c = (char)v;
+                        break;
+                    }
+                    default: return fail("bad escape");
+                }
+            }
+            out.push_back(c);
+        }
+        if (p >= end) return fail("unterminated string");
+        ++p;
+        return true;
+    }
+    bool value(Json& v, int depth = 0) {
+        if (depth > 32) return fail("nesting too deep");
+        ws();
+        if (p >= end) return fail("unexpected end of input");
+        if (*p == '{') {
+            v.kind = Json::Obj;
+            ++p, ws();
+            if (p < end && *p == '}') { ++p; return true; }
+            for (;;) {
+                ws();
+                std::string key;
+                if (!string(key)) return false;
+                ws();
+                if (p >= end || *p != ':') return fail("expected ':'");
+                ++p;
+                Json child;
+                if (!value(child, depth + 1)) return false;
+                v.obj.emplace_back(std::move(key), std::move(child));
+                ws();
+                if (p < end && *p == ',') { ++p; continue; }
+                if (p < end && *p == '}') { ++p; return true; }
+                return fail("expected ',' or '}'");
+            }
+        }
+        if (*p == '[') {
+            v.kind = Json::Arr;
+            ++p, ws();
+            if (p < end && *p == ']') { ++p; return true; }
+            for (;;) {
+                Json child;
+                if (!value(child, depth + 1)) return false;
+                v.arr.push_back(std::move(child));
+                ws();
+                if (p < end && *p == ',') { ++p; continue; }
+                if (p < end && *p == ']') { ++p; return true; }
+                return fail("expected ',' or ']'");
+            }
+        }
+        if (*p == '"') { v.kind = Json::Str; return string(v.str); }
+        if (end - p >= 4 && std::strncmp(p, "true", 4) == 0) { v.kind = Json::Bool, v.b = true, p += 4; return true; }
+        if (end - p >= 5 && std::strncmp(p, "false", 5) == 0) { v.kind = Json::Bool, p += 5; return true; }
+        if (end - p >= 4 && std::strncmp(p, "null", 4) == 0) { p += 4; return true; }
+        char* stop = nullptr;
+        const std::string tail(p, (size_t)(end - p) < 64 ? (size_t)(end - p) : 64);
+        v.num = std::strtod(tail.c_str(), &stop);
+        if (stop == tail.c_str()) return fail("unexpected character");
+        v.kind = Json::Num;
+        p += stop - tail.c_str();
+        return true;
+    }
+};
+inline bool json_u32(const Json* j, uint32_t& out) {
+    if (!j || j->kind != Json::Num || j->num < 0 || j->num > 4294967295.0 || j->num != (double)(uint64_t)j->num) return false;
+    out = (uint32_t)j->num;
+    return true;
+}
+inline bool json_str(const Json* j, std::string& out) {
+    if (!j || j->kind != Json::Str) return false;
+    out = j->str;
+    return true;
+}
+inline bool scalar_ty_from(const std::string& s, ScalarTy& t) {
+    if (s == "U8") t = ScalarTy::U8; else if (s == "F32") t = ScalarTy::F32; else if (s == "U32") t = ScalarTy::U32;
+    else t = ScalarTy::Other;   // the other axc-hir scalar types exist; none of this backend's kernels binds them
+    return true;
+}
+inline DispatchError metadata_error(ErrorKind k, std::string msg) {
+    DispatchError e;
+    e.kind = k, e.message = std::move(msg);
+    return e;
+}
+}  // namespace detail
+
+// metadata.rs:107-122.
+inline Result<KernelMetadata> load_kernel_metadata(const std::string& path) {
+    using namespace detail;
+    std::FILE* f = std::fopen(path.c_str(), "rb");
+    if (!f) return metadata_error(ErrorKind::MetadataIoError, "metadata I/O error: cannot open " + path);
+    std::string text;
+    char buf[4096];
+    size_t n;
+    while ((n = std::fread(buf, 1, sizeof buf, f)) > 0) text.append(buf, n);
+    const bool read_ok = !std::ferror(f);
+    std::fclose(f);
+    if (!read_ok) return metadata_error(ErrorKind::MetadataIoError, "metadata I/O error: read failed: " + path);
+
+    JsonReader rd{text.data(), text.data() + text.size(), {}};
+    Json root;
+    bool ok = rd.value(root);
+    if (ok) { rd.ws(); if (rd.p != rd.end) ok = rd.fail("trailing characters"); }
+    auto parse_error = [&](const std::string& what) {
+        return metadata_error(ErrorKind::MetadataParseError, "metadata parse error: " + what);
+    };
+    if (!ok || root.kind != Json::Obj) return parse_error(ok ? "top level is not an object" : rd.err);
+    KernelMetadata m;
+    if (!json_u32(root.get("schema_version"), m.schema_version)) return parse_error("missing field `schema_version`");
+    if (!json_str(root.get("kernel_name"), m.kernel_name)) return parse_error("missing field `kernel_name`");
+    if (!json_str(root.get("entry_point"), m.entry_point)) return parse_error("missing field `entry_point`");
+    if (!json_u32(root.get("push_constant_total_bytes"), m.push_constant_total_bytes))
+        return parse_error("missing field `push_constant_total_bytes`");
+    const Json* wg = root.get("workgroup_size");
+    if (!wg || wg->kind != Json::Arr || wg->arr.size() != 3) return parse_error("`workgroup_size` must be an array of 3");
+    for (int i = 0; i < 3; ++i)
+        if (!json_u32(&wg->arr[i], m.workgroup_size[i])) return parse_error("`workgroup_size` entries must be u32");
+    const Json* plan = root.get("binding_plan");
+    if (!plan || plan->kind != Json::Obj) return parse_error("missing field `binding_plan`");
+    const Json* bufs = plan->get("buffers");
+    const Json* scal = plan->get("scalars");
+    if (!bufs || bufs->kind != Json::Arr || !scal || scal->kind != Json::Arr ||
+        !json_u32(plan->get("push_constant_total_bytes"), m.binding_plan.push_constant_total_bytes))
+        return parse_error("`binding_plan` needs buffers, scalars and push_constant_total_bytes");
+    for (const Json& b : bufs->arr) {
+        BufferBindingSlot s{};
+        std::string elem, access;
+        const Json* ty = b.get("ty");
+        if (b.kind != Json::Obj || !json_str(b.get("name"), s.name) || !ty || !json_str(ty->get("elem"), elem) ||
+            !json_str(ty->get("access"), access) || !json_u32(b.get("position"), s.position) ||
+            !json_u32(b.get("buffer_position"), s.buffer_position))
+            return parse_error("malformed buffer binding slot");
+        scalar_ty_from(elem, s.ty.elem);
+        if (access == "ReadOnly") s.ty.access = BufferAccess::ReadOnly;
+        else if (access == "ReadWrite") s.ty.access = BufferAccess::ReadWrite;
+        else if (access == "WriteOnly") s.ty.access = BufferAccess::WriteOnly;
+        else return parse_error("unknown variant `" + access + "` of BufferAccess");
+        m.binding_plan.buffers.push_back(std::move(s));
+    }
+    for (const Json& c : scal->arr) {
+        ScalarPushConstantSlot s{};
+        std::string ty;
+        if (c.kind != Json::Obj || !json_str(c.get("name"), s.name) || !json_str(c.get("ty"), ty) ||
+            !json_u32(c.get("offset"), s.offset) || !json_u32(c.get("member_index"), s.member_index) ||
+            !json_u32(c.get("position"), s.position))
+            return parse_error("malformed scalar push-constant slot");
+        scalar_ty_from(ty, s.ty);
+        m.binding_plan.scalars.push_back(std::move(s));
+    }
+    if (m.schema_version != CURRENT_SCHEMA_VERSION) {
+        DispatchError e = metadata_error(ErrorKind::MetadataSchemaMismatch,
+                                         "metadata schema version mismatch: got " + std::to_string(m.schema_version) +
+                                             ", supported " + std::to_string(CURRENT_SCHEMA_VERSION));
+        e.provided = m.schema_version, e.expected = CURRENT_SCHEMA_VERSION;
+        return e;
+    }
+    return m;
+}
 
 inline bool probe_vulkan_available() { return axc_cuda_probe() == 1; }   // icd.rs:22-38
 inline bool gpu_tests_enabled() {                                         // icd.rs:40-48

@@ -9,6 +9,7 @@
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
+#include <string>
 
 #include "axc_runtime.hpp"
 
@@ -31,8 +32,65 @@ static bool read_fixture(const char* path, uint32_t n, std::vector<uint8_t>& q, 
     return ok;
 }
 
+static bool write_text(const char* path, const char* text) {
+    std::FILE* f = std::fopen(path, "wb");
+    if (!f) return false;
+    const bool ok = std::fputs(text, f) >= 0;
+    std::fclose(f);
+    return ok;
+}
+
+// metadata.rs tests: round trip of a v1 sidecar, other versions rejected with got / supported,
+// malformed text and a missing file are typed errors.
+static int metadata_cases(const char* dir) {
+    using namespace axc;
+    const std::string base = std::string(dir) + "/axc_meta_test";
+    const char* good =
+        "{\n  \"schema_version\": 1,\n  \"kernel_name\": \"q4km_dequant_matvec\",\n  \"workgroup_size\": [64, 1, 1],\n"
+        "  \"binding_plan\": {\"buffers\": ["
+        "{\"name\": \"q\", \"ty\": {\"elem\": \"U8\", \"access\": \"ReadOnly\"}, \"position\": 0, \"buffer_position\": 0},"
+        "{\"name\": \"x\", \"ty\": {\"elem\": \"F32\", \"access\": \"ReadOnly\"}, \"position\": 1, \"buffer_position\": 1},"
+        "{\"name\": \"y\", \"ty\": {\"elem\": \"F32\", \"access\": \"ReadWrite\"}, \"position\": 2, \"buffer_position\": 2}],"
+        " \"scalars\": [{\"name\": \"n_superblocks\", \"ty\": \"U32\", \"offset\": 0, \"member_index\": 0, \"position\": 3}],"
+        " \"push_constant_total_bytes\": 4},\n  \"push_constant_total_bytes\": 4,\n  \"entry_point\": \"q4km_dequant_matvec\"\n}\n";
+    CHECK(write_text((base + ".json").c_str(), good));
+    auto r = load_kernel_metadata(base + ".json");
+    CHECK(r.is_ok());
+    const KernelMetadata& m = r.unwrap();
+    CHECK(m.schema_version == CURRENT_SCHEMA_VERSION && m.kernel_name == "q4km_dequant_matvec" && m.entry_point == m.kernel_name);
+    CHECK(m.workgroup_size[0] == 64 && m.workgroup_size[1] == 1 && m.workgroup_size[2] == 1 && m.push_constant_total_bytes == 4);
+    CHECK(m.binding_plan.hash64() == q4_matvec_binding_plan().hash64());   // the plan both Q4 kernels compile to
+    const uint32_t wg[3] = {64, 1, 1};
+    const KernelMetadata made = KernelMetadata::new_("k", wg, q4_matvec_binding_plan(), "k");
+    CHECK(made.schema_version == 1 && made.push_constant_total_bytes == 4);
+
+    std::string v2 = good;
+    v2.replace(v2.find("\"schema_version\": 1"), 19, "\"schema_version\": 2");
+    CHECK(write_text((base + "_v2.json").c_str(), v2.c_str()));
+    auto r2 = load_kernel_metadata(base + "_v2.json");
+    CHECK(r2.is_err() && r2.unwrap_err().kind == ErrorKind::MetadataSchemaMismatch);
+    CHECK(r2.unwrap_err().provided == 2 && r2.unwrap_err().expected == 1);
+
+    CHECK(write_text((base + "_bad.json").c_str(), "{\"schema_version\": 1, \"kernel_name\": "));
+    auto r3 = load_kernel_metadata(base + "_bad.json");
+    CHECK(r3.is_err() && r3.unwrap_err().kind == ErrorKind::MetadataParseError);
+    std::string noentry = good;
+    noentry.replace(noentry.find("\"entry_point\""), 13, "\"entry_pointx\"");
+    CHECK(write_text((base + "_noentry.json").c_str(), noentry.c_str()));
+    auto r4 = load_kernel_metadata(base + "_noentry.json");
+    CHECK(r4.is_err() && r4.unwrap_err().kind == ErrorKind::MetadataParseError);
+    auto r5 = load_kernel_metadata(base + "_does_not_exist.json");
+    CHECK(r5.is_err() && r5.unwrap_err().kind == ErrorKind::MetadataIoError);
+    for (const char* suffix : {".json", "_v2.json", "_bad.json", "_noentry.json"}) std::remove((base + suffix).c_str());
+    return 0;
+}
+
 static int host_only() {
     using namespace axc;
+    {
+        const char* tmp = std::getenv("TMPDIR");
+        if (metadata_cases(tmp && *tmp ? tmp : "/tmp") != 0) return 1;
+    }
     CHECK(kDispatchErrorVariantCount == 25);
     const ParamBindingPlan plan = q4_matvec_binding_plan();
     CHECK(plan.buffers.size() == 3 && plan.scalars.size() == 1 && plan.push_constant_total_bytes == 4);

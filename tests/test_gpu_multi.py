@@ -111,8 +111,23 @@ def _decode_worker(rank, world, port, out_dir):
             outs, d, h1, ksum = oracle.decode_token(weights, shape.hidden, shape.kv, shape.ffn, h0,
                                                     normalise_input=False)
             _y64, mag = oracle.matvec_rows_f64("q4k", weights[0][0], h0, shape.hidden + 2 * shape.kv, shape.hidden // 256)
-            got0 = sweep.output(0, 0).cpu().numpy()
-            assert (np.abs(got0 - outs[0][0]) / mag).max() <= 1e-5, mode   # every rank's slice of the first linear
+            if mode == "paired":
+                # this rank's rows of q, k, v (the per-kernel bar) ...
+                hq, hk, _hf = sweep.slices
+                hid, kv = shape.hidden, shape.kv
+                idx = np.concatenate([np.arange(rank * hq, (rank + 1) * hq), hid + np.arange(rank * hk, (rank + 1) * hk),
+                                      hid + kv + np.arange(rank * hk, (rank + 1) * hk)])
+                got0 = sweep.local_output(0, 0).cpu().numpy()
+                assert (np.abs(got0 - outs[0][0][idx]) / mag[idx]).max() <= 1e-5, mode
+                # ... and the sum of EVERY rank's partial products: o before its input's unit-RMS scale
+                q_full = outs[0][0][:hid]
+                o_raw = oracle.matvec_rows("q4k", weights[0][1], q_full, hid, hid // 256)
+                _o64, omag = oracle.matvec_rows_f64("q4k", weights[0][1], q_full, hid, hid // 256)
+                got1 = sweep.local_output(0, 1).cpu().numpy()
+                assert (np.abs(got1 - o_raw) / omag).max() <= 2e-5, mode
+            else:
+                got0 = sweep.output(0, 0).cpu().numpy()
+                assert (np.abs(got0 - outs[0][0]) / mag).max() <= 1e-5, mode   # every rank's slice of the first linear
             for layer in range(shape.layers):
                 for j in sweep.checkable_outputs:
                     got, ref = sweep.output(layer, j).cpu().numpy(), outs[layer][j]

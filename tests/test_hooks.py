@@ -145,7 +145,30 @@ def test_correctness_policy_parse():
     P = hooks.CorrectnessPolicy
     assert P.parse("none") == P("None") and P.parse("bit-exact") == P("BitExact")
     assert P.parse("fp-tol:4") == P("EquivFpTol", 4)
-    assert P.parse("fp-tol:x") == P("None") and P.parse("whatever") == P("None")
+    assert P.parse("fp-tol:x") == P("EquivFpTol", 4) and P.parse("whatever") == P("None")   # optimize.rs:121-135
+
+
+def test_policy_is_applied_to_the_output_bytes():
+    """A variant one unit in the last place away from the ordinal-0 variant: rejected under
+    bit-exact, accepted under fp-tol:1, rejected again under fp-tol:0 (grid_search.rs:54-75)."""
+    import numpy as np
+    ref = np.array([1.0, -2.5, 0.0, 1e-3], np.float32)
+    got = ref.copy()
+    got.view(np.uint32)[1] += 1
+    P = hooks.CorrectnessPolicy
+    assert hooks.policy_failure(P.parse("none"), got.tobytes(), ref.tobytes()) is None
+    assert hooks.policy_failure(P.parse("bit-exact"), ref.tobytes(), ref.tobytes()) is None
+    assert hooks.policy_failure(P.parse("bit-exact"), got.tobytes(), ref.tobytes()) == ("BitMismatch", 1)
+    assert hooks.policy_failure(P.parse("fp-tol:1"), got.tobytes(), ref.tobytes()) is None
+    assert hooks.policy_failure(P.parse("fp-tol:0"), got.tobytes(), ref.tobytes()) == ("UlpExceeded", 1, 1)
+    assert hooks.policy_failure(P.parse("bit-exact"), got.tobytes(), ref.tobytes()[:8])[0] == "OracleError"
+    # and through grid_search: the rejected variant cannot win however fast it is
+    outs = {32: got.tobytes(), 64: ref.tobytes()}
+    fail = lambda a: hooks.policy_failure(P.parse("bit-exact"), outs[a["workgroup_x"]], outs[64])
+    r = hooks.grid_search({"workgroup_x": [64, 32]}, P.parse("bit-exact"), fail,
+                          lambda a: _stats(100 if a["workgroup_x"] == 32 else 900))
+    assert r.winner_assignments == {"workgroup_x": 64}
+    assert r.results[1].outcome == ("CorrectnessRejected", ("BitMismatch", 1))
 
 
 def test_tuning_from_assignments_rejects_unknown_holes():
