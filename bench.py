@@ -575,17 +575,29 @@ def run_e2e(pkg, device_index, leg, args, world, dist, dev):
                             [0, 0, rows_local * 4], pc)
         handles.append(h)
     x_buf = bytearray(x_host.tobytes())   # the caller's host buffer: read again on every dispatch
-    y_full = torch.empty(rows_local * world, dtype=torch.float32, device=dev) if world > 1 else None
     bound = [ctx.bind(handles[m], (rows_local, 1, 1), [b"", x_buf, b""], [0, 0, rows_local * 4], pc)
              for m in range(N_MATRICES)]
+    if world > 1:
+        # every rank's host ends a pass with all 16 assembled vectors: the 16 slices of a pass go to the
+        # device in one copy and are exchanged by one NCCL all-gather (the runtime call itself is
+        # single-GPU, as in the reference; assembling is the caller's step)
+        stage = torch.empty(N_MATRICES * rows_local, dtype=torch.float32).pin_memory()
+        stage_np = stage.numpy()
+        y_loc = torch.empty(N_MATRICES * rows_local, dtype=torch.float32, device=dev)
+        y_all = torch.empty(world * N_MATRICES * rows_local, dtype=torch.float32, device=dev)
+        y_all_host = torch.empty(world * N_MATRICES * rows_local, dtype=torch.float32).pin_memory()
 
     def one_pass():
         out = None
         for m in range(N_MATRICES):
             out = bound[m].run()
             if world > 1:
-                y_loc = torch.frombuffer(out[2], dtype=torch.float32).to(dev, non_blocking=True)
-                dist.all_gather_into_tensor(y_full, y_loc)
+                stage_np[m * rows_local:(m + 1) * rows_local] = np.frombuffer(out[2], np.float32)
+        if world > 1:
+            y_loc.copy_(stage, non_blocking=True)
+            dist.all_gather_into_tensor(y_all, y_loc)
+            y_all_host.copy_(y_all, non_blocking=True)
+            torch.cuda.current_stream().synchronize()
         return out
 
     # result check (checker only): the last call's y against the device-resident path
@@ -616,11 +628,15 @@ def run_e2e(pkg, device_index, leg, args, world, dist, dev):
         h.drop()
     ctx.drop()
     cps = args.passes_per_step * N_MATRICES
-    return {"value": round(val, 3), "unit": UNIT, "h2d_bytes_per_step": cps * K_COLS * 4,
-            "d2h_bytes_per_step": cps * rows_local * 4, "us_per_call": round(dt / (passes * N_MATRICES) * 1e6, 3),
+    extra = cps * rows_local * 4 if world > 1 else 0             # the slices going back up for the exchange
+    back = cps * rows_local * 4 * world if world > 1 else 0       # the assembled vectors coming down
+    return {"value": round(val, 3), "unit": UNIT, "h2d_bytes_per_step": cps * K_COLS * 4 + extra,
+            "d2h_bytes_per_step": cps * rows_local * 4 + back, "us_per_call": round(dt / (passes * N_MATRICES) * 1e6, 3),
             "calls_timed": passes * N_MATRICES,
             "api": "CudaContext.dispatch_handle (axc_cuda_dispatch), one handle per matrix, weights resident via "
-                   "the empty-input rule, x from and y to host buffers on every call, sequential calls on one thread"}
+                   "the empty-input rule, x from and y to host buffers on every call, sequential calls on one thread"
+                   + ("; per pass the 16 slices are exchanged by one NCCL all-gather and the assembled vectors "
+                      "copied back to the host" if world > 1 else "")}
 
 
 # ------------------------------------------------------------------------------------------------
@@ -943,7 +959,11 @@ def run_decode(args):
     ms_tok = float(ms.item()) / steps
     if status != 0:
         raise SystemExit(f"rank {rank}: kernel status {status}")
+    kv_checksum = float(sweep.kv_checksum().item())   # every rank: may reduce over the ranks
+    if world > 1:
+        dist.barrier()
     if rank != 0:
+        dist.destroy_process_group()
         return
     weight_bytes = shape.bytes_per_layer * shape.layers
     peaks = measured_peaks()
@@ -958,7 +978,7 @@ def run_decode(args):
                    "weight_bytes": weight_bytes, "exchange": sweep.mode, "launch": "cuda_graph" if graph is not None else "stream",
                    "l2": "inputs larger than L2: every token streams all weights once",
                    "parallelism": "single GPU" if world == 1 else sweep.parallelism},
-        "aggregate_gbs": round(agg, 1), "kv_checksum": float(sweep.kv_checksum().item()),
+        "aggregate_gbs": round(agg, 1), "kv_checksum": kv_checksum,
         "us_per_layer": round(ms_tok * 1e3 / shape.layers, 2),
         "peer_slice_check": {"what": "summed partial products of every rank (o of layer 0), 3 x 32 rows" if sweep.mode == "paired"
                              else f"first linear, {rs} rows of each of the {decode.CHUNKS} row chunks (every rank's slice)",
@@ -970,6 +990,8 @@ def run_decode(args):
         "gpu_launches": steps * sweep.launches_per_token, "clocks": sampler.summary(float(ms.item())),
     }
     print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
 
 
 def run_prefill(args):
