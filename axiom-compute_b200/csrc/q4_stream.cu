@@ -128,16 +128,16 @@ __device__ __forceinline__ void signal_cta_done(const StreamParams& p, uint32_t 
         const uint32_t n4 = p.rows >> 2;
         const float4* src = reinterpret_cast<const float4*>(p.y);
         float4* dst = reinterpret_cast<float4*>(p.y_host);
-        // loads in batches of eight before their stores: the loop is latency-bound otherwise
-        for (uint32_t base = 0; base < n4; base += 8u * blockDim.x) {
-            float4 v[8];
+        // loads in batches of sixteen before their stores: the loop is latency-bound otherwise
+        for (uint32_t base = 0; base < n4; base += 16u * blockDim.x) {
+            float4 v[16];
 #pragma unroll
-            for (int u = 0; u < 8; ++u) {
+            for (int u = 0; u < 16; ++u) {
                 const uint32_t i = base + u * blockDim.x + tid;
                 if (i < n4) v[u] = __ldcg(src + i);
             }
 #pragma unroll
-            for (int u = 0; u < 8; ++u) {
+            for (int u = 0; u < 16; ++u) {
                 const uint32_t i = base + u * blockDim.x + tid;
                 if (i < n4) dst[i] = v[u];
             }
@@ -536,6 +536,23 @@ __global__ void __launch_bounds__(512, 1) q4_matvec_stream_kernel(const StreamPa
     // Weights never depend on an earlier kernel.  When this CTA was scheduled early (programmatic
     // dependent launch, previous grid still running) the first ring-full of weights is fetched
     // while it waits for that grid.
+    // A CTA that produces the x image from host memory (single-launch host dispatch) issues its
+    // loads of the first 64 positions first: the PCIe round trip then runs while thread 0 requests
+    // the ring.
+    [[maybe_unused]] float4 host_first[8];
+    [[maybe_unused]] bool host_first_valid = false;
+    if constexpr (PREPARED) {
+        if (p.x_host && bid < p.x_n_prod && blockDim.x >= 128u) {
+            const float4* xh = reinterpret_cast<const float4*>(p.x_host);
+            const uint32_t n_f4 = p.n_pos * 16u;
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+                const uint32_t idx = u * blockDim.x + tid, gi = bid * 1024u + idx;
+                host_first[u] = idx < 1024u && gi < n_f4 ? __ldg(xh + gi) : make_float4(0.f, 0.f, 0.f, 0.f);
+            }
+            host_first_valid = true;
+        }
+    }
     if (p.prefetch_first) start_stream();
 
     // x may be the output of the previous kernel in the stream; y may still be read by it.
@@ -572,10 +589,15 @@ __global__ void __launch_bounds__(512, 1) q4_matvec_stream_kernel(const StreamPa
                 for (uint32_t pos0 = bid * 64u; pos0 < p.x_pitch; pos0 += p.x_n_prod * 64u) {
                     for (uint32_t base = 0; base < 1024u; base += 8u * blockDim.x) {   // one round for >= 128 threads
                         float4 v[8];
+                        if (host_first_valid && pos0 == bid * 64u) {   // already on their way (base is 0 here)
 #pragma unroll
-                        for (int u = 0; u < 8; ++u) {
-                            const uint32_t idx = base + u * blockDim.x + tid, gi = pos0 * 16u + idx;
-                            v[u] = idx < 1024u && gi < n_f4 ? __ldg(xh + gi) : make_float4(0.f, 0.f, 0.f, 0.f);
+                            for (int u = 0; u < 8; ++u) v[u] = host_first[u];
+                        } else {
+#pragma unroll
+                            for (int u = 0; u < 8; ++u) {
+                                const uint32_t idx = base + u * blockDim.x + tid, gi = pos0 * 16u + idx;
+                                v[u] = idx < 1024u && gi < n_f4 ? __ldg(xh + gi) : make_float4(0.f, 0.f, 0.f, 0.f);
+                            }
                         }
 #pragma unroll
                         for (int u = 0; u < 8; ++u) {
@@ -595,10 +617,14 @@ __global__ void __launch_bounds__(512, 1) q4_matvec_stream_kernel(const StreamPa
                 }
                 __threadfence();
                 __syncthreads();
-                if (tid == 0 && atomicAdd(p.x_prod_counter, 1u) == p.x_n_prod - 1u) {
-                    *p.x_prod_counter = 0;
-                    __threadfence();
-                    asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(p.x_ready), "r"(p.x_seq) : "memory");
+                if (tid == 0) {
+                    bool last = p.x_n_prod == 1u;   // a single producer publishes at once
+                    if (!last && atomicAdd(p.x_prod_counter, 1u) == p.x_n_prod - 1u) {
+                        *p.x_prod_counter = 0;
+                        __threadfence();
+                        last = true;
+                    }
+                    if (last) asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(p.x_ready), "r"(p.x_seq) : "memory");
                 }
             }
             if (tid == 0) {

@@ -28,6 +28,8 @@
 #include <cudaTypedefs.h>
 #include <cuda_bf16.h>
 
+#include <mutex>
+
 #include "axc_device.cuh"
 #include "axc_kernels.h"
 
@@ -457,8 +459,19 @@ cudaError_t launch_q4k_prefill(const uint8_t* q, const uint16_t* a_bf16, float* 
             return cudaErrorInvalidValue;
     }
     auto kern = pair ? q4k_prefill_kernel<true> : q4k_prefill_kernel<false>;
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)PF_SMEM);
-    if (e != cudaSuccess) return e;
+    {   // raise the dynamic shared-memory limit once per device and kernel form, not on every call
+        static std::mutex mu;
+        static bool done[64][2] = {};
+        int dev = 0;
+        cudaError_t e = cudaGetDevice(&dev);
+        if (e != cudaSuccess) return e;
+        std::lock_guard<std::mutex> lock(mu);
+        if (dev < 0 || dev >= 64 || !done[dev][pair ? 1 : 0]) {
+            e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)PF_SMEM);
+            if (e != cudaSuccess) return e;
+            if (dev >= 0 && dev < 64) done[dev][pair ? 1 : 0] = true;
+        }
+    }
     cudaLaunchConfig_t cfg{};
     // pair: an even number of CTAs; a trailing CTA without rows of its own still holds its share of the tokens
     cfg.gridDim = dim3(pair ? (tiles + 1u) & ~1u : tiles, (m_tokens + PF_TOK_MAX - 1) / PF_TOK_MAX);

@@ -434,8 +434,12 @@ def run_ours(args):
     # the previous launch).  The strict figure (pdl = 2: x is read only after the previous
     # launch has completed, as a dependent decode chain needs) is measured beside it.
     pdl_mode = args.pdl if args.pdl >= 0 else 3
-    tuning = ops.make_tuning(pdl=pdl_mode)
-    tuning_strict = ops.make_tuning(pdl=2)
+    extra = {}
+    for item in filter(None, args.tune.split(",")):      # launch tunables for experiments: "threads=256,resident=2"
+        k, v = item.split("=")
+        extra[k.strip()] = int(v)
+    tuning = ops.make_tuning(pdl=pdl_mode, **extra)
+    tuning_strict = ops.make_tuning(pdl=2, **extra)
 
     # ---- parity before timing (checker only): every rank, every rank's slice ----
     peer_err = leg.check()
@@ -541,7 +545,7 @@ def run_ours(args):
         "data": "synthetic",
         "config": bench_config(world, strong or world == 1),
         "calls_per_step": pps * N_MATRICES, "passes_per_step": pps, "timed_region_ms": round(elapsed_ms, 3),
-        "launch": {"mode": "cuda_graph of one pass, replayed" if use_graph else "stream",
+        "launch": {"mode": "cuda_graph of one pass, replayed" if use_graph else "stream", "tune": args.tune or "default",
                    "dependency": {3: "independent calls (shared x, distinct y): pdl=3", 2: "strict stream order: pdl=2",
                                   1: "strict stream order: pdl=1", 0: "no programmatic dependent launch"}[pdl_mode],
                    "rows_per_gpu": leg.rows_local, "global_rows": leg.rows_global,
@@ -624,6 +628,34 @@ def run_e2e(pkg, device_index, leg, args, world, dist, dev):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     dt = float(t.item())
     val = passes * N_MATRICES * leg.bytes_per_call_local * world / dt / 1e9
+
+    # Beside it (N = 1): the same calls issued from several host threads.  Dispatches on different
+    # handles may run concurrently (crates/axc-runtime/src/context.rs:494-497); each call is still a
+    # complete host-to-host round trip, the threads only overlap their launch and completion latencies.
+    concurrent = None
+    if world == 1 and args.e2e_threads > 1:
+        from concurrent.futures import ThreadPoolExecutor
+        nt = args.e2e_threads
+        per = [bound[i::nt] for i in range(nt)]
+
+        def worker(mine, n_pass):
+            for _ in range(n_pass):
+                for b in mine:
+                    b.run()
+
+        with ThreadPoolExecutor(nt) as pool:
+            list(pool.map(lambda mine: worker(mine, 8), per))
+            t0 = time.perf_counter()
+            list(pool.map(lambda mine: worker(mine, passes), per))
+            dtc = time.perf_counter() - t0
+        ok = all(np.array_equal(np.frombuffer(bytes(bound[m].outputs[2]), np.float32),
+                                leg.ops.q4k_matvec(leg.weights[m], leg.x_dev, rows_local, N_SB).cpu().numpy())
+                 for m in range(N_MATRICES))
+        if not ok:
+            raise SystemExit("e2e: concurrent dispatches returned a wrong result")
+        concurrent = {"threads": nt, "value": round(passes * N_MATRICES * leg.bytes_per_call_local / dtc / 1e9, 3),
+                      "unit": UNIT, "us_per_call": round(dtc / (passes * N_MATRICES) * 1e6, 3),
+                      "note": "same calls, different handles dispatched concurrently from host threads; results checked"}
     for h in handles:
         h.drop()
     ctx.drop()
@@ -632,7 +664,7 @@ def run_e2e(pkg, device_index, leg, args, world, dist, dev):
     back = cps * rows_local * 4 * world if world > 1 else 0       # the assembled vectors coming down
     return {"value": round(val, 3), "unit": UNIT, "h2d_bytes_per_step": cps * K_COLS * 4 + extra,
             "d2h_bytes_per_step": cps * rows_local * 4 + back, "us_per_call": round(dt / (passes * N_MATRICES) * 1e6, 3),
-            "calls_timed": passes * N_MATRICES,
+            "calls_timed": passes * N_MATRICES, "concurrent": concurrent,
             "api": "CudaContext.dispatch_handle (axc_cuda_dispatch), one handle per matrix, weights resident via "
                    "the empty-input rule, x from and y to host buffers on every call, sequential calls on one thread"
                    + ("; per pass the 16 slices are exchanged by one NCCL all-gather and the assembled vectors "
@@ -1051,8 +1083,11 @@ def main():
                     help="N > 1: all-gather fused into the matvec epilogue, or NCCL after each call")
     ap.add_argument("--force-graph", action="store_true", help="CUDA graph even with NCCL collectives in the pass")
     ap.add_argument("--pdl", type=int, default=-1, help="programmatic dependent launch mode (0 off, 1, 2, 3; -1 default)")
+    ap.add_argument("--tune", default="", help="matvec launch tunables, e.g. threads=256,ctas_per_sm=1,resident=2 "
+                                               "(fields of axc_tuning; default: the library's choice)")
     ap.add_argument("--skip-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--skip-e2e", action="store_true", help="skip the host-buffer leg (profiling)")
+    ap.add_argument("--e2e-threads", type=int, default=4, help="host threads of the concurrent e2e sub-figure (N = 1)")
     ap.add_argument("--skip-sub", action="store_true", help="skip the sub-records of the other configurations")
     ap.add_argument("--skip-weak", action="store_true", help="N > 1: skip the weak-scaling sub-record")
     ap.add_argument("--sub-decode-layers", type=int, default=8, help="layers in the decode-sweep sample sub-record")
