@@ -19,7 +19,7 @@ next linear's input is the ``mode``:
   still running when the source is (value, epoch) words) assembles x once, quantises it to the
   digit-word image and leaves the sums of x^2; every CTA of the consumer reads its digit words
   straight into registers.
-* ``"fused"`` (default on several GPUs): every consumer CTA assembles and quantises x itself (``axc_cuda_q4k_matvec_fused``);
+* ``"fused"``: every consumer CTA assembles and quantises x itself (``axc_cuda_q4k_matvec_fused``);
   with more than one GPU a finish kernel first unpacks the words into a plain vector.
 * ``"mixed"`` (default on one GPU): "prepared" for the linears with K > 8192 (the down projection),
   "fused" for the others: the faster choice per shape on one GPU.  On several GPUs it runs (the
@@ -27,7 +27,7 @@ next linear's input is the ``mode``:
   5.73 ms/token on two GPUs).
 * ``"poll"``: as "fused", but every consumer CTA polls the (value, epoch) words itself (no launch in
   between, 2 x the bytes per CTA past L1: measured slower).
-* ``"paired"`` (several GPUs only): the linears are sharded in pairs so that a layer has two exchanges
+* ``"paired"`` (several GPUs only, the default there when the shape divides): the linears are sharded in pairs so that a layer has two exchanges
   instead of four.  qkv and gate+up are sharded by ROWS, each rank owning matching slices (its
   rows of q, k and v; its rows of g and of u); o and down are sharded by COLUMNS: a rank multiplies
   its column range of Wo with its own slice of q (of Wdown with its own g + u), which it has
@@ -111,10 +111,14 @@ class DecodeSweep:
 
     def __init__(self, shape: SweepShape, device, seed: int = 0xA0C0 + 4 * 16, group=None, tuning=None,
                  mode: str = "auto"):
-        if mode == "auto":   # the faster one as measured: mixed on one GPU, fused + finish on several
+        if mode == "auto":   # the faster one as measured: mixed on one GPU, paired sharding on several
             multi = torch.distributed.is_available() and torch.distributed.is_initialized() \
                 and torch.distributed.get_world_size(group) > 1
-            mode = "fused" if multi else "mixed"
+            mode = "mixed"
+            if multi:
+                w = torch.distributed.get_world_size(group)
+                fits = shape.hidden % (256 * w) == 0 and shape.ffn % (256 * w) == 0 and shape.kv % w == 0
+                mode = "paired" if fits else "fused"
         if mode not in MODES:
             raise ValueError(f"mode must be one of {MODES}")
         self.shape, self.device = shape, torch.device(device)
