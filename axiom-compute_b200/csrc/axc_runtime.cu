@@ -290,14 +290,20 @@ bool wait_flag(const volatile uint32_t* flag, uint32_t seq, uint64_t timeout_ms,
     const auto t0 = clock::now();
     const auto limit = std::chrono::milliseconds(timeout_ms);
     for (uint32_t spins = 1;; ++spins) {
-        if (*flag == seq) return true;
+        if (*flag == seq) {
+            std::atomic_thread_fence(std::memory_order_acquire);   // y and the status word are read after the flag
+            return true;
+        }
 #if defined(__x86_64__) || defined(__i386__)
         __builtin_ia32_pause();
 #endif
         if ((spins & 1023u) == 0) {
             const cudaError_t q = cudaStreamQuery(st);
             if (q == cudaSuccess) {           // everything queued has finished
-                if (*flag == seq) return true;
+                if (*flag == seq) {
+                    std::atomic_thread_fence(std::memory_order_acquire);
+                    return true;
+                }
                 *err = cudaErrorUnknown;      // the kernel ended without signalling
                 return false;
             }

@@ -2,7 +2,7 @@
 
 The byte layouts of the kernels' ``q`` buffers are ggml's ``block_q4_K`` (144 bytes per 256
 weights) and ``block_q4_0`` (18 bytes per 32 weights), which is what the reference's kernels were
-written against (DESIGN.md:442-451 of the reference); a Q4_K / Q4_0 tensor stored in a GGUF file is
+written against (the design notes of the reference repository, lines 442-451 of its top-level design file); a Q4_K / Q4_0 tensor stored in a GGUF file is
 therefore consumed as it lies in the file: one row of the matrix = ``ne[0] / block`` consecutive
 blocks, rows consecutive, no repacking.  This module reads the container (header, metadata,
 tensor directory) and hands out such tensors as byte views plus the (rows, blocks per row) the

@@ -163,6 +163,14 @@ void axc_cuda_kernel_set_tuning(axc_kernel* k, const struct axc_tuning* tuning);
  *   hold; workgroups = [1,1,1] is exactly the reference's single-output behaviour, and
  *   n = 0 writes y[0] = +0.0.
  *   The wait for completion is bounded by the fence timeout -> AXC_ERR_FENCE_TIMEOUT.
+ *   Two ways through a dispatch, with the same results.  With stats == NULL, resident or freshly given
+ *   inputs, at least 64 rows, no input binding read back and a row length the streaming kernel serves
+ *   (Q4_K_M up to 128 superblocks, Q4_0 an even number of blocks up to 1024), a dispatch is ONE kernel
+ *   launch: x is read from its pinned, device-mapped staging buffer by the kernel's first CTAs, y is copied
+ *   into mapped host memory by its last CTA, and completion is a sequence number polled in mapped host
+ *   memory (no copy-engine transfer, no event).  Otherwise (device timing asked for, strict handles, other
+ *   shapes, or AXC_DISPATCH_FAST=0 in the environment) inputs go through cudaMemcpyAsync and completion
+ *   through a CUDA event.
  */
 int axc_cuda_dispatch(axc_ctx* ctx, axc_kernel* k, const uint32_t workgroups[3],
                       const void* const* inputs, const size_t* input_lens, uint32_t n_inputs,

@@ -491,7 +491,7 @@ def test_fixed_point_worst_case_stays_inside_its_derived_bound(ops, synth):
 
 
 def test_rows_whose_dequantised_weights_are_all_zero(ops, synth):
-    """Rows the reference computes as exactly 0.0 (every dequantised weight is 0), judged by its
+    """Rows the reference computes as exactly 0.0 (every dequantised weight is 0), measured by its
     own rule: |cpu| <= 1e-10, so the ABSOLUTE difference counts
     (crates/axc-driver/tests/compile_q4km_dequant_matvec.rs:946-950).
     Q4_0: all nibbles 8 -> (8 - 8) * d = 0; the kernel sums (q - 8) X in integers, so it returns
