@@ -94,9 +94,12 @@ def test_grid_search_tool_ranks_tunable_variants(mcp, tmp_path):
     rows, n = 2048, 16
     sizes = [rows * n * 144, n * 256 * 4, rows * 4]
     mcp2 = hooks.McpContext(cuda=mcp.cuda, git_sha="abc1234", history_dir=str(tmp_path))
+    # policy "none": every variant is still checked against the reference-order kernel by bench_variant
+    # (correctness.kind below); the policies that compare variants with the ordinal-0 variant are
+    # exercised further down (tile heights change the order of the row sum, so they are not bit-equal)
     req = hooks.GridSearchRequest(sizes, 5, {"tile_rows": [8, 16], "stages": [2, 3]},
                                   metadata=hooks.q4_metadata("q4km_dequant_matvec"),
-                                  correctness="fp-tol:4", push_constants_base64=b64(n))
+                                  correctness="none", push_constants_base64=b64(n))
     resp = hooks.grid_search_tool(req, mcp2)
     assert len(resp.ranked) == 4 and all(v.outcome == "ok" and v.correctness.kind == "Ok" for v in resp.ranked)
     meds = [v.median_ns for v in resp.ranked]
@@ -107,6 +110,32 @@ def test_grid_search_tool_ranks_tunable_variants(mcp, tmp_path):
     rec = [json.loads(l) for l in open(resp.history_path)]
     assert len(rec) == 1 and rec[0]["grid_search"]["winner_variant_id"] == resp.winner_variant_id
     assert rec[0]["grid_search"]["ranked"][0]["correctness"] == {"status": "ok"}
+
+
+def test_grid_search_tool_applies_the_stated_policy(mcp):
+    """bit-exact / fp-tol compare each variant's output bytes with the ordinal-0 variant's
+    (grid_search.rs:54-75).  The ring depth does not touch the arithmetic, so those variants pass
+    bit-exact; a variant may only be rejected with the failure its policy defines, and a rejected
+    variant never wins."""
+    rows, n = 2048, 16
+    sizes = [rows * n * 144, n * 256 * 4, rows * 4]
+    meta = hooks.q4_metadata("q4km_dequant_matvec")
+    same = hooks.grid_search_tool(hooks.GridSearchRequest(sizes, 3, {"stages": [2, 3, 4]}, metadata=meta,
+                                                          correctness="bit-exact", push_constants_base64=b64(n)), mcp)
+    assert all(v.outcome == "ok" for v in same.ranked)
+    mixed = hooks.grid_search_tool(hooks.GridSearchRequest(sizes, 3, {"tile_rows": [8, 16], "stages": [2, 3]},
+                                                           metadata=meta, correctness="bit-exact",
+                                                           push_constants_base64=b64(n)), mcp)
+    by_assign = {tuple(sorted(v.assignments.items())): v for v in mixed.ranked}
+    assert by_assign[(("stages", 2), ("tile_rows", 8))].outcome == "ok"       # ordinal 0 against itself
+    assert by_assign[(("stages", 3), ("tile_rows", 8))].outcome == "ok"       # same arithmetic
+    for v in mixed.ranked:
+        assert v.outcome == "ok" or v.outcome.startswith("correctness_rejected: ('BitMismatch'"), v.outcome
+    assert by_assign[tuple(sorted(mixed.winner_assignments.items()))].outcome == "ok"
+    loose = hooks.grid_search_tool(hooks.GridSearchRequest(sizes, 3, {"tile_rows": [8, 16]}, metadata=meta,
+                                                           correctness="fp-tol:4294967295",
+                                                           push_constants_base64=b64(n)), mcp)
+    assert all(v.outcome == "ok" for v in loose.ranked)
 
 
 def test_run_optimize_writes_winner_metadata_and_strategy_sidecar(mcp, tmp_path):
