@@ -237,6 +237,8 @@ class BenchVariantRequest:
     workgroup_override: Optional[Sequence[int]] = None
     push_constants_base64: Optional[str] = None
     output_sizes: Optional[Sequence[int]] = None
+    input_seed: Optional[int] = None   # inputs are seeded by the variant id (bench_variant.rs:252-256) unless a
+                                       # caller that compares variants with each other fixes the seed
 
 
 @dataclass
@@ -324,10 +326,11 @@ def bench_variant(req: BenchVariantRequest, ctx: McpContext) -> BenchVariantResp
     workgroups = derive_workgroups(req.input_sizes, meta.workgroup_size, req.workgroup_override,
                                    kernel_name=meta.kernel_name, push_constants=pc, output_sizes=output_sizes)
     variant_id = compute_variant_id(req.assignments)
+    seed = variant_id if req.input_seed is None else int(req.input_seed)
     if meta.kernel_name in Q4_KERNELS and len(pc) >= 4:
-        inputs = seeded_q4_inputs(meta.kernel_name, req.input_sizes, struct.unpack_from("<I", pc)[0], variant_id)
+        inputs = seeded_q4_inputs(meta.kernel_name, req.input_sizes, struct.unpack_from("<I", pc)[0], seed)
     else:
-        inputs = seeded_inputs(req.input_sizes, variant_id)
+        inputs = seeded_inputs(req.input_sizes, seed)
     # Distinct spirv words per variant keep the cache keys of differently tuned handles apart.
     handle = cuda.prepare_kernel([0x07230203, variant_id & 0xFFFFFFFF, variant_id >> 32], plan,
                                  plan.push_constant_total_bytes, meta.entry_point)
@@ -537,20 +540,22 @@ def grid_search_tool(req: GridSearchRequest, ctx: McpContext) -> GridSearchRespo
     policy = CorrectnessPolicy.parse(req.correctness)
     responses: Dict[int, BenchVariantResponse] = {}
 
+    first = enumerate_strategy(dict(req.holes))[0].assignments if req.holes else {}
+    # a policy that compares variants needs all of them to see the same inputs: those of ordinal 0
+    shared_seed = compute_variant_id(first) if policy.kind != "None" else None
+
     def run(assignments) -> BenchVariantResponse:
         vid = compute_variant_id(assignments)
         if vid not in responses:
             responses[vid] = bench_variant(BenchVariantRequest(
                 req.input_sizes, req.sample_count, metadata=meta, assignments=dict(assignments),
                 workgroup_override=req.workgroup_override, push_constants_base64=req.push_constants_base64,
-                output_sizes=req.output_sizes), ctx)
+                output_sizes=req.output_sizes, input_seed=shared_seed), ctx)
         return responses[vid]
 
     def bench_fn(assignments) -> SampleStats:
         r = run(assignments)
         return SampleStats(r.median_ns, min(r.samples), max(r.samples), len(r.samples))
-
-    first = enumerate_strategy(dict(req.holes))[0].assignments if req.holes else {}
 
     def correctness_fn(assignments):
         r = run(assignments)
