@@ -184,6 +184,35 @@ static int with_gpu(double expected, const char* fixture_path) {
     std::memcpy(&y2, out.unwrap()[2].data(), 4);
     CHECK(y2 == y1);
 
+    // rows from the grid: 64 copies of the fixture row, resident after the first call; the calls with an
+    // empty q take the single-launch path (x read from host memory by the kernel, completion polled):
+    // every row must give the fixture's value, call after call, also after x changes
+    {
+        const uint32_t rows = 64;
+        std::vector<uint8_t> q64((size_t)rows * q.size());
+        for (uint32_t r = 0; r < rows; ++r) std::memcpy(q64.data() + (size_t)r * q.size(), q.data(), q.size());
+        const uint32_t wg64[3] = {rows, 1, 1};
+        auto hr64 = ctx.prepare_kernel({0x07230203u, 64u}, plan, 4, "q4km_dequant_matvec");
+        CHECK(hr64.is_ok());
+        KernelHandle h64 = hr64.unwrap();
+        auto o64 = ctx.dispatch_handle(h64, wg64, {{q64.data(), q64.size()}, {x.data(), x.size() * 4}, {nullptr, 0}},
+                                       {0, 0, (size_t)rows * 4}, pc);
+        CHECK(o64.is_ok());
+        std::vector<float> x2(x);
+        for (int it = 0; it < 6; ++it) {
+            const float scale = it % 2 ? 0.5f : 1.0f;
+            for (size_t i = 0; i < x.size(); ++i) x2[i] = x[i] * scale;
+            o64 = ctx.dispatch_handle(h64, wg64, {{nullptr, 0}, {x2.data(), x2.size() * 4}, {nullptr, 0}},
+                                      {0, 0, (size_t)rows * 4}, pc);
+            CHECK(o64.is_ok() && o64.unwrap()[2].size() == (size_t)rows * 4);
+            for (uint32_t r = 0; r < rows; ++r) {
+                float yr;
+                std::memcpy(&yr, o64.unwrap()[2].data() + 4 * r, 4);
+                CHECK(std::fabs((double)yr - expected * scale) <= 1e-5 * std::fabs(expected * scale));
+            }
+        }
+    }
+
     // a clone keeps the kernel usable after the context is gone (AT-827): release must not crash
     KernelHandle survivor = h;
     {

@@ -1,6 +1,7 @@
-"""GGUF ingestion: the reader against files written by the module's own writer (no file from
-another tool is available: container parity is unpinned), and the Q4 tensors it hands out
-against the oracle / the GPU kernels."""
+"""GGUF ingestion: the reader against files written by the module's own writer and against a
+file assembled field by field from the published layout (no file from another tool is available:
+container parity stays unpinned), and the Q4 tensors it hands out against the oracle / the GPU
+kernels."""
 import struct
 
 import numpy as np
@@ -101,3 +102,38 @@ def test_matvec_on_a_tensor_read_from_gguf(sample, ops, synth):
     y_ref = oracle.matvec_rows("q4k", qk, x, rows, n)
     _y, mag = oracle.matvec_rows_f64("q4k", qk, x, rows, n)
     assert (np.abs(y - y_ref) / mag).max() <= 1e-5
+
+
+def test_reader_on_bytes_assembled_by_hand_from_the_specification(tmp_path, synth):
+    """A file laid out field by field here, independently of the module's writer, following the
+    published GGUF v3 layout: magic "GGUF", u32 version, u64 tensor count, u64 key-value count;
+    key-values as (string key, u32 value type, value) with strings as u64 length + bytes; tensor
+    infos as (string name, u32 n_dims, u64 dims..., u32 ggml type, u64 offset into the data
+    section); the data section starts at the next multiple of general.alignment (default 32)."""
+    def gstr(t):
+        b = t.encode()
+        return struct.pack("<Q", len(b)) + b
+
+    qk = synth.q4k_weights(3, 2, 6101)           # 3 rows x 512 columns of Q4_K: 3 * 2 * 144 bytes
+    q0 = synth.q4_0_weights(2, 4, 6102)          # 2 rows x 128 columns of Q4_0: 2 * 4 * 18 bytes
+    body = b"GGUF" + struct.pack("<IQQ", 3, 2, 3)
+    body += gstr("general.architecture") + struct.pack("<I", 8) + gstr("llama")        # 8 = string
+    body += gstr("llama.block_count") + struct.pack("<II", 4, 7)                       # 4 = uint32
+    body += gstr("x.list") + struct.pack("<IIQ", 9, 5, 3) + struct.pack("<iii", -1, 0, 9)   # 9 = array of int32 (5)
+    off0, off1 = 0, (len(qk) + 31) // 32 * 32
+    body += gstr("a.weight") + struct.pack("<IQQ", 2, 512, 3) + struct.pack("<IQ", 12, off0)    # 12 = Q4_K
+    body += gstr("b.weight") + struct.pack("<IQQ", 2, 128, 2) + struct.pack("<IQ", 2, off1)     # 2 = Q4_0
+    body += b"\0" * (-len(body) % 32)
+    data = qk.tobytes() + b"\0" * (off1 - len(qk)) + q0.tobytes()
+    path = tmp_path / "by_hand.gguf"
+    path.write_bytes(body + data)
+    with gguf.GgufFile(path) as g:
+        assert g.version == 3 and g.alignment == 32 and g.data_start == len(body)
+        assert g.metadata == {"general.architecture": "llama", "llama.block_count": 7, "x.list": [-1, 0, 9]}
+        a, b = g.tensors["a.weight"], g.tensors["b.weight"]
+        assert (a.shape, a.type_name, a.nbytes) == ((512, 3), "Q4_K", 3 * 2 * 144)
+        assert (b.shape, b.type_name, b.nbytes) == ((128, 2), "Q4_0", 2 * 4 * 18)
+        assert np.array_equal(g.tensor_bytes("a.weight"), qk) and np.array_equal(g.tensor_bytes("b.weight"), q0)
+        fmt, rows, n, qa = g.q4_matrix("a.weight")
+        assert (fmt, rows, n) == ("q4k", 3, 2) and np.array_equal(np.asarray(qa).reshape(-1), qk)
+        assert g.q4_matrix("b.weight")[:3] == ("q4_0", 2, 4)
