@@ -18,19 +18,20 @@
 // read and y written only after it.
 //
 // Arithmetic.  The 4-bit weights stay integers.  Per CTA the activations are quantised ONCE to
-// 23-bit signed fixed point relative to the largest |x| of each 64-column chunk (a power-of-two
-// scale: an error of at most 2^-23 of the chunk maximum per element, below what an fp32
-// accumulation of the row keeps), and the three low bytes of that integer are used as base-256
-// digits (two unsigned, the top one signed), transposed so that one 32-bit word holds one digit
-// of four neighbouring columns.  A thread owns one 64-weight position of the row (Q4_K_M:
+// 24-bit two's-complement fixed point relative to the largest |x| of each 64-column chunk (a
+// power-of-two scale: an error of at most 2^-23 of the chunk maximum per element, below what an
+// fp32 accumulation of the row keeps; the bound is derived beside X_FRAC_BITS), and the three
+// bytes of that integer are used as base-256 digits (two unsigned, the top one signed),
+// transposed so that one 32-bit word holds one digit of four neighbouring columns.  A thread owns one 64-weight position of the row (Q4_K_M:
 // superblock s, chunk c = 32 nibble bytes, sub-blocks 2c and 2c+1; Q4_0: a pair of blocks) for
 // the life of the CTA and keeps its 48 digit words in registers.  Per 32-bit word of nibbles:
 // `w & 0x0F0F0F0F` is the four low nibbles as bytes, `w & 0xF0F0F0F0` the four high ones times
 // 16 (the 1/16 is folded into the scale), and six dp4a (u8 x u8/s8, exact int32 accumulation)
 // multiply them with the digit words: two logic instructions and six integer-dot instructions
 // per eight weights, nothing converted per weight.  Per sub-block the exact integer sum is
-// rescaled once and combined as d*sc*sum(q_i x_i) - dmin*m*sum(x_i) (Q4_0: d*(sum(q_i x_i) -
-// 8*sum(x_i))), so weights are never materialised here (the bit-exact dequantised values come
+// rescaled once and combined as d*sc*sum(q_i X_i) - dmin*m*sum(X_i) over the same fixed-point X
+// (Q4_0: d*sum((q_i - 8) X_i), the -8 folded into the start value of the integer sums), so weights
+// are never materialised here (the bit-exact dequantised values come
 // from the dequant kernels, which share the unpack code).  Row sums: transposed warp-shuffle
 // reduction, per-warp partials in shared memory, one fixed-order combine per CTA at the end
 // (deterministic).
