@@ -1026,6 +1026,65 @@ def run_decode(args):
         dist.destroy_process_group()
 
 
+def run_allgather_share(args):
+    """`--workload allgather_share` (N > 1): one pass of the row-sharded matvec as the headline times it
+    (16 calls with the all-gather epilogue + the finish launch) against the 16 calls alone, for the
+    strong and the weak split: the share of the exchange step's finish launch and the NVLink bytes."""
+    import torch
+    import torch.distributed as dist
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if world < 2:
+        raise SystemExit("allgather_share needs more than one rank (launch with torch.distributed.run)")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+    import datetime
+    dist.init_process_group("nccl", device_id=dev, timeout=datetime.timedelta(seconds=180))
+    pkg = importlib.import_module("axiom-compute_b200")
+    ops = importlib.import_module("axiom-compute_b200.ops")
+    base = base_matrix()
+    x_host = pkg.synth.activations(K_COLS, pkg.synth.config_seed(2, 1))
+    tn = ops.make_tuning(pdl=3)
+    out = {}
+    for strong in (True, False):
+        leg = MatvecLeg(torch, dist, pkg, world, rank, dev, base, x_host, strong, "fused")
+        leg.check(matrices=(0,))
+
+        def matvecs_only():
+            for m in range(N_MATRICES):
+                leg.gather.matvec(leg.weights[m], leg.x_dev, N_SB, m, status=leg.status, tuning=tn)
+
+        res = {}
+        for name, fn in (("pass_with_finish_us", lambda: leg.one_pass(tn)), ("matvec_launches_only_us", matvecs_only)):
+            side = torch.cuda.Stream(device=dev)
+            side.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(side):
+                fn()
+            torch.cuda.current_stream().wait_stream(side)
+            torch.cuda.synchronize()
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, capture_error_mode="thread_local"):
+                fn()
+            ms = time_graph(torch, dist, world, dev, g.replay, args.passes_per_step, max(2, min(args.steps, 8)), 1)
+            res[name] = round(ms * 1e3 / (max(2, min(args.steps, 8)) * args.passes_per_step), 3)
+            if name == "matvec_launches_only_us":
+                leg.gather.finish(leg.status)     # end the step the replays left open
+                torch.cuda.synchronize()
+        res["finish_launch_us"] = round(res["pass_with_finish_us"] - res["matvec_launches_only_us"], 3)
+        res["nvlink_bytes_out_per_gpu_per_pass"] = N_MATRICES * leg.rows_local * 8 * (world - 1)
+        res["rows_per_gpu"] = leg.rows_local
+        if int(leg.status.item()) != 0:
+            raise SystemExit(f"rank {rank}: kernel status {int(leg.status.item())}")
+        out["strong" if strong else "weak"] = res
+        del leg
+    dist.barrier()
+    if rank == 0:
+        print(json.dumps({"metric": "allgather_finish_share", "n_gpus": world, "calls_per_pass": N_MATRICES, **out}), flush=True)
+    dist.destroy_process_group()
+
+
 def run_prefill(args):
     """`--workload prefill`: the batched-prefill contraction (M = 512 tokens, K = 4096, N = 14336;
     tensor-pipe bound), 8 distinct weight matrices round-robin.  Single GPU."""
@@ -1063,7 +1122,7 @@ def run_prefill(args):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--workload", choices=["matvec", "decode70b", "prefill"], default="matvec",
+    ap.add_argument("--workload", choices=["matvec", "decode70b", "prefill", "allgather_share"], default="matvec",
                     help="matvec: the headline 14336 x 4096 metric; decode70b: the 70B-shaped decode sweep")
     ap.add_argument("--layers", type=int, default=80, help="decode70b: layers in the stack")
     ap.add_argument("--prefill-strict", action="store_true",
@@ -1098,6 +1157,8 @@ def main():
         run_decode(args)
     elif args.workload == "prefill":
         run_prefill(args)
+    elif args.workload == "allgather_share":
+        run_allgather_share(args)
     else:
         run_ours(args)
 
