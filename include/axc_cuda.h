@@ -224,9 +224,11 @@ typedef struct axc_tuning {
                             still be in flight, which is every launch from the most recent ordered
                             one (inclusive; any kernel not of this library counts as ordered) up
                             to this call.  Only the final store of y waits for the launch before,
-                            and the launch is shaped to overlap its neighbours (one small CTA per
-                            SM, up to four launches resident).  Example: producer of x, gate
-                            projection (pdl 2), up projection of the same x (pdl 3). */
+                            and the launch is shaped for a RUN of such launches (one small CTA on
+                            every second SM, up to four launches resident per SM): a lone
+                            independent launch uses half the machine.  Example: producer of x, then
+                            the matrices that consume it, the first with pdl 2, the others with
+                            pdl 3. */
     int32_t resident;    /* CTAs per SM the shared-memory budget is cut for; 0 = default */
 } axc_tuning;
 
