@@ -64,7 +64,7 @@ def test_launch_plan_geometry(ops):
     assert p["grid"] == 296 and p["block"] == 256 and p["smem"] <= 114 * 1024   # 2 CTAs per SM
     assert p["tile_rows"] * p["stages"] >= 32           # most of a CTA's 48-49 rows in flight
     p = ops.q4k_matvec_plan(4096, 56)
-    assert p["block"] == 224                            # 7 warps cover the 56 superblocks
+    assert p["block"] % 224 == 0 and p["block"] <= 512   # groups of 7 warps cover the 56 superblocks
     p = ops.q4k_matvec_plan(8192, 112)
     assert p["grid"] == 148 and p["block"] == 448 and p["smem"] <= 227 * 1024
     p = ops.q4k_matvec_plan(1, 128)
