@@ -1085,21 +1085,36 @@ __global__ void gather_finish_kernel(const uint64_t* __restrict__ pairs, const u
     asm volatile("ld.relaxed.gpu.global.u32 %0, [%1];" : "=r"(epoch) : "l"(epoch_ptr) : "memory");
     pairs += (size_t)(epoch & 1u) * (parity_stride >> 3);
     bool gave_up = false, ahead = false;
-    for (uint32_t i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) {
-        uint64_t w = 0;
-        uint32_t it = gave_up ? (1u << 22) - 1u : 0u;   // after one timeout the rest get a single look
-        for (; it < (1u << 22); ++it) {
-            asm volatile("ld.relaxed.sys.global.b64 %0, [%1];" : "=l"(w) : "l"(pairs + i) : "memory");
-            const int32_t d = (int32_t)((uint32_t)(w >> 32) - epoch);
-            if (d == 0) break;
-            if (d > 0) {
-                ahead = true;
-                break;
-            }
-            __nanosleep(100);
+    // Eight words per thread are requested together (one round trip to L2 for all of them when they
+    // have arrived, which is the common case); a word that has not is then polled on its own.
+    const uint32_t stride = gridDim.x * blockDim.x;
+    for (uint32_t base = blockIdx.x * blockDim.x + threadIdx.x; base < n; base += 8u * stride) {
+        uint64_t w8[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+            const uint32_t i = base + (uint32_t)u * stride;
+            w8[u] = 0;
+            if (i < n) asm volatile("ld.relaxed.sys.global.b64 %0, [%1];" : "=l"(w8[u]) : "l"(pairs + i) : "memory");
         }
-        if (it == (1u << 22)) gave_up = true;
-        out[i] = __uint_as_float((uint32_t)w);
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+            const uint32_t i = base + (uint32_t)u * stride;
+            if (i >= n) continue;
+            uint64_t w = w8[u];
+            int32_t d = (int32_t)((uint32_t)(w >> 32) - epoch);
+            if (d < 0) {
+                uint32_t it = gave_up ? (1u << 22) - 1u : 0u;   // after one timeout the rest get a single look
+                for (; it < (1u << 22); ++it) {
+                    __nanosleep(100);
+                    asm volatile("ld.relaxed.sys.global.b64 %0, [%1];" : "=l"(w) : "l"(pairs + i) : "memory");
+                    d = (int32_t)((uint32_t)(w >> 32) - epoch);
+                    if (d >= 0) break;
+                }
+                if (it == (1u << 22)) gave_up = true;
+            }
+            if (d > 0) ahead = true;
+            out[i] = __uint_as_float((uint32_t)w);
+        }
     }
     if (status) {
         if (gave_up) atomicOr(status, ERR_PEER_WAIT_TIMEOUT);
@@ -1153,14 +1168,20 @@ __global__ void gather_reduce_finish_kernel(const uint64_t* __restrict__ pairs, 
         float part[16];
         uint32_t it = gave_up ? (1u << 22) - 1u : 0u;
         for (; pending && it < (1u << 22); ++it) {
+            // all pending parts are requested before the first is looked at: one round trip, not one per part
+            uint64_t w[16];
+#pragma unroll
+            for (uint32_t r = 0; r < 16u; ++r) {
+                w[r] = 0;
+                if (r < n_parts && (pending >> r & 1u))
+                    asm volatile("ld.relaxed.sys.global.b64 %0, [%1];" : "=l"(w[r]) : "l"(pairs + r * stride_w + i) : "memory");
+            }
 #pragma unroll
             for (uint32_t r = 0; r < 16u; ++r) {
                 if (r < n_parts && (pending >> r & 1u)) {
-                    uint64_t w;
-                    asm volatile("ld.relaxed.sys.global.b64 %0, [%1];" : "=l"(w) : "l"(pairs + r * stride_w + i) : "memory");
-                    const int32_t d = (int32_t)((uint32_t)(w >> 32) - epoch);
+                    const int32_t d = (int32_t)((uint32_t)(w[r] >> 32) - epoch);
                     if (d >= 0) {
-                        part[r] = __uint_as_float((uint32_t)w);
+                        part[r] = __uint_as_float((uint32_t)w[r]);
                         pending &= ~(1u << r);
                         ahead = ahead || d > 0;
                     }
