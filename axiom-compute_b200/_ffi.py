@@ -30,6 +30,7 @@ AXC_ERR_STAGING_COPY_FAILED = 25
 AXC_ERR_INVALID_ARGUMENT = 100
 
 AXC_FINISH_OVERLAP_PREVIOUS = 1
+AXC_FINISH_LET_NEXT_START = 2
 AXC_TY_OTHER, AXC_TY_U8, AXC_TY_F32, AXC_TY_U32 = 0, 1, 2, 3
 AXC_ACCESS_READ_ONLY, AXC_ACCESS_READ_WRITE, AXC_ACCESS_WRITE_ONLY = 1, 2, 3
 

@@ -91,12 +91,18 @@ class PeerGather:
                 C.byref(tuning) if tuning is not None else None)
         _raise_for(rc)
 
-    def finish(self, status: Optional[torch.Tensor] = None, slots: Optional[int] = None) -> None:
+    def finish(self, status: Optional[torch.Tensor] = None, slots: Optional[int] = None,
+               let_next_start: bool = False) -> None:
         """Wait for the step's words of the first `slots` slots (default all), unpack them, and end
-        the step (handshake with the other ranks, epoch advanced): one launch."""
+        the step (handshake with the other ranks, epoch advanced): one launch.  `let_next_start`:
+        the launches behind this one (the next step's matvecs, declared independent) may be
+        scheduled while it still waits, so a stream or graph of several steps does not drain at
+        the end of each; they must not read ``vector()`` before an ordered launch."""
         n = (self.slots if slots is None else int(slots)) * self.rows_global
+        flags = _ffi.AXC_FINISH_LET_NEXT_START if let_next_start else 0
         with torch.cuda.device(self.device):
             rc = _ffi.lib().axc_cuda_gather_finish(
                 self.pairs.data_ptr(), self.epoch.data_ptr(), self.values.data_ptr(), n, self._stream(),
-                status.data_ptr() if status is not None else None, 0, self.parity_stride, C.byref(self._sync))
+                status.data_ptr() if status is not None else None, flags, self.parity_stride,
+                C.byref(self._sync))
         _raise_for(rc)

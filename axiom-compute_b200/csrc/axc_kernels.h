@@ -108,7 +108,7 @@ cudaError_t launch_q4k_prefill(const uint8_t* q, const uint16_t* a_bf16, float* 
 
 cudaError_t launch_gather_finish(const uint64_t* pairs, const uint32_t* epoch_ptr, float* out, uint32_t n,
                                  uint32_t* status, cudaStream_t stream, bool overlap, uint64_t parity_stride = 0,
-                                 const GatherSync* sync = nullptr);
+                                 const GatherSync* sync = nullptr, bool let_next_start = false);
 cudaError_t launch_gather_next_epoch(uint32_t* epoch_ptr, cudaStream_t stream);
 // out[i] = sum over parts r < n_parts of the value of word pairs[r * part_stride / 8 + i] (K-sharded linears).
 cudaError_t launch_gather_reduce_finish(const uint64_t* pairs, const uint32_t* epoch_ptr, float* out, uint32_t n,

@@ -1063,7 +1063,7 @@ int axc_cuda_gather_finish(const uint64_t* pairs, const uint32_t* epoch, float* 
     }
     return launch_result(axc::launch_gather_finish(pairs, epoch, out, n, status, (cudaStream_t)stream,
                                                    (flags & AXC_FINISH_OVERLAP_PREVIOUS) != 0, parity_stride_bytes,
-                                                   sync ? &gs : nullptr));
+                                                   sync ? &gs : nullptr, (flags & AXC_FINISH_LET_NEXT_START) != 0));
 }
 
 int axc_cuda_gather_reduce_finish(const uint64_t* pairs, const uint32_t* epoch, float* out, uint32_t n,

@@ -1079,8 +1079,13 @@ struct FinishSync {
 __global__ void gather_finish_kernel(const uint64_t* __restrict__ pairs, const uint32_t* __restrict__ epoch_ptr,
                                      float* __restrict__ out, uint32_t n, uint32_t* status, uint32_t overlap,
                                      uint64_t parity_stride, const FinishSync sync) {
-    if (!overlap) asm volatile("griddepcontrol.wait;" ::: "memory");
-    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");   // ordered: only after the wait
+    // bit 0 of `overlap`: do not wait for the launch before this one; bit 1: let the launches behind
+    // this one be scheduled at once (they then overlap this kernel as independent matvec launches
+    // overlap each other: the caller states that they read nothing this launch writes before their
+    // own dependency wait).
+    if (overlap & 2u) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    if (!(overlap & 1u)) asm volatile("griddepcontrol.wait;" ::: "memory");
+    if (!(overlap & 2u)) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");   // ordered: only after the wait
     uint32_t epoch;
     asm volatile("ld.relaxed.gpu.global.u32 %0, [%1];" : "=r"(epoch) : "l"(epoch_ptr) : "memory");
     pairs += (size_t)(epoch & 1u) * (parity_stride >> 3);
@@ -1225,10 +1230,13 @@ cudaError_t launch_gather_reduce_finish(const uint64_t* pairs, const uint32_t* e
 
 cudaError_t launch_gather_finish(const uint64_t* pairs, const uint32_t* epoch_ptr, float* out, uint32_t n,
                                  uint32_t* status, cudaStream_t stream, bool overlap, uint64_t parity_stride,
-                                 const GatherSync* gs) {
+                                 const GatherSync* gs, bool let_next_start) {
     if (n == 0 && !gs) return cudaSuccess;
     uint32_t blocks = (n + 255) / 256;
-    if (blocks > 592) blocks = 592;
+    // A launch that lets its successors start sits on the SMs beside them while it waits for the
+    // launch before it: one CTA per SM, so that it does not take their registers.
+    const uint32_t cap = let_next_start ? 148u : 592u;
+    if (blocks > cap) blocks = cap;
     if (blocks < 1) blocks = 1;
     FinishSync fs{};
     if (gs) {
@@ -1241,8 +1249,8 @@ cudaError_t launch_gather_finish(const uint64_t* pairs, const uint32_t* epoch_pt
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr, cfg.numAttrs = 1;
-    return cudaLaunchKernelEx(&cfg, gather_finish_kernel, pairs, epoch_ptr, out, n, status, overlap ? 1u : 0u,
-                              parity_stride, fs);
+    return cudaLaunchKernelEx(&cfg, gather_finish_kernel, pairs, epoch_ptr, out, n, status,
+                              (overlap ? 1u : 0u) | (let_next_start ? 2u : 0u), parity_stride, fs);
 }
 
 cudaError_t launch_gather_next_epoch(uint32_t* epoch_ptr, cudaStream_t stream) {

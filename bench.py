@@ -49,6 +49,10 @@ K_COLS = N_SB * 256
 ROW_BYTES = N_SB * 144
 N_MATRICES = 16
 PASSES_PER_STEP = 128
+# Passes captured in one CUDA graph.  A graph launch starts only after the one before it has
+# completed, so with independent calls (which overlap each other on every SM) a one-pass graph
+# drains and refills the GPU every 16 calls: 5.65 us per call against 5.16 with 16 passes per graph.
+PASSES_PER_GRAPH = 16
 Q_BYTES = ROWS * ROW_BYTES
 ALGO_BYTES_PER_CALL = Q_BYTES + K_COLS * 4 + ROWS * 4   # 33 103 872
 METRIC = "q4k_matvec_14336x4096_effective_bandwidth"
@@ -321,6 +325,7 @@ class MatvecLeg:
                 w = build_matrix(base, m, rank if world > 1 else 0)
             self.weights.append(torch.from_numpy(np.ascontiguousarray(w).reshape(-1)).to(dev))
         self.gather, self.collective = None, "none"
+        self.finish_early = True
         if world > 1:
             self.collective = collective
             if collective == "fused":
@@ -337,7 +342,9 @@ class MatvecLeg:
         if self.gather is not None:
             for m in range(N_MATRICES):
                 self.gather.matvec(self.weights[m], self.x_dev, N_SB, m, status=self.status, tuning=tn)
-            self.gather.finish(self.status)   # every all-gather of the pass is complete inside the timed region
+            # every all-gather of the pass is complete inside the timed region; with calls declared
+            # independent the next pass's matvecs may start while this launch still waits for the words
+            self.gather.finish(self.status, let_next_start=self.finish_early and tn.pdl == 3)
             return
         for m in range(N_MATRICES):
             self.ops.q4k_matvec(self.weights[m], self.x_dev, self.rows_local, N_SB, y=self.y_local[m],
@@ -380,10 +387,17 @@ class MatvecLeg:
                                          f"rank {r}, rows {begin + off}..: norm-wise error {err:.3e}")
         return worst
 
-    def graph_for(self, tn_key, tn, use_graph):
+    def graph_for(self, tn_key, tn, use_graph, passes=1):
+        """A callable that runs `passes` passes: a CUDA graph of them, replayed, or plain launches."""
         torch = self.torch
+
+        def run_passes():
+            for _ in range(passes):
+                self.one_pass(tn)
+
         if not use_graph:
-            return lambda: self.one_pass(tn)
+            return run_passes
+        tn_key = (tn_key, passes)
         if tn_key not in self.graphs:
             side = torch.cuda.Stream(device=self.dev)
             side.wait_stream(torch.cuda.current_stream())
@@ -394,7 +408,7 @@ class MatvecLeg:
             torch.cuda.synchronize()
             g = torch.cuda.CUDAGraph()
             with torch.cuda.graph(g, capture_error_mode="thread_local"):
-                self.one_pass(tn)
+                run_passes()
             self.graphs[tn_key] = g
         return self.graphs[tn_key].replay
 
@@ -462,11 +476,14 @@ def run_ours(args):
     # With NCCL collectives in the pass the default is plain stream launches: capturing the NCCL
     # all-gather together with programmatic-dependent-launch kernels hung on this stack.
     use_graph = not args.no_graph and (world == 1 or leg.gather is not None or args.force_graph)
-    run_pass = leg.graph_for("main", tuning, use_graph)
     pps = max(1, args.passes_per_step)
+    ppg = max(1, args.passes_per_graph)
+    if pps % ppg:
+        raise SystemExit("--passes-per-step must be a multiple of --passes-per-graph")
+    run_pass = leg.graph_for("main", tuning, use_graph, ppg)
     warm = max(args.warmup, 3)
     sampler = ClockSampler(local_rank)
-    elapsed_ms = time_graph(torch, dist, world, dev, run_pass, pps, args.steps, warm, sampler)
+    elapsed_ms = time_graph(torch, dist, world, dev, run_pass, pps // ppg, args.steps, warm, sampler)
     if int(leg.status.item()) != 0:
         raise SystemExit(f"kernel status {int(leg.status.item())} after the timed region")
 
@@ -476,9 +493,9 @@ def run_ours(args):
 
     strict = None
     if world == 1 and pdl_mode == 3:
-        run2 = leg.graph_for("strict", tuning_strict, use_graph)
+        run2 = leg.graph_for("strict", tuning_strict, use_graph, ppg)
         n2 = max(2, min(args.steps, 8))
-        ms2 = time_graph(torch, dist, world, dev, run2, pps, n2, 1)
+        ms2 = time_graph(torch, dist, world, dev, run2, pps // ppg, n2, 1)
         us2 = ms2 * 1e3 / (n2 * pps * N_MATRICES)
         strict = {"us_per_call": round(us2, 4), "value": round(leg.bytes_per_call_local / us2 / 1e3, 2), "unit": UNIT,
                   "frac_of_measured_peak": round(leg.bytes_per_call_local / us2 / 1e3 / peaks["hbm"], 4),
@@ -490,9 +507,9 @@ def run_ours(args):
     if world > 1 and strong and not args.skip_weak:
         wleg = MatvecLeg(torch, dist, pkg, world, rank, dev, base, x_host, False, collective)
         werr = wleg.check(matrices=(0,))
-        wrun = wleg.graph_for("main", tuning, use_graph)
+        wrun = wleg.graph_for("main", tuning, use_graph, ppg)
         wsteps = max(2, min(args.steps, 6))
-        wms = time_graph(torch, dist, world, dev, wrun, pps, wsteps, 1)
+        wms = time_graph(torch, dist, world, dev, wrun, pps // ppg, wsteps, 1)
         wcalls = wsteps * pps * N_MATRICES
         weak = {"metric": "q4k_matvec_weak_scaling_14336_rows_per_gpu_effective_bandwidth",
                 "value": round(wcalls * wleg.bytes_per_call_local * world / (wms * 1e-3) / 1e9, 2), "unit": UNIT,
@@ -545,7 +562,7 @@ def run_ours(args):
         "data": "synthetic",
         "config": bench_config(world, strong or world == 1),
         "calls_per_step": pps * N_MATRICES, "passes_per_step": pps, "timed_region_ms": round(elapsed_ms, 3),
-        "launch": {"mode": "cuda_graph of one pass, replayed" if use_graph else "stream", "tune": args.tune or "default",
+        "launch": {"mode": f"cuda_graph of {ppg} pass(es), replayed" if use_graph else "stream", "tune": args.tune or "default",
                    "dependency": {3: "independent calls (shared x, distinct y): pdl=3", 2: "strict stream order: pdl=2",
                                   1: "strict stream order: pdl=1", 0: "no programmatic dependent launch"}[pdl_mode],
                    "rows_per_gpu": leg.rows_local, "global_rows": leg.rows_global,
@@ -728,14 +745,19 @@ def _matvec_sub(torch, ops, synth, dev, peaks, fmt, rows, n, seed_cfg, label):
                 fn(ws[m], x, rows, n, y=ys[m], status=st, tuning=tn)
         torch.cuda.current_stream().wait_stream(side)
         torch.cuda.synchronize()
+        # several rounds over the matrices per graph: a graph launch starts only after the one before
+        # it has completed, so a short graph of independent calls would drain the GPU at every replay
+        reps = max(1, -(-128 // n_mat))
         g = torch.cuda.CUDAGraph()
         with torch.cuda.graph(g):
-            for m in range(n_mat):
-                fn(ws[m], x, rows, n, y=ys[m], status=st, tuning=tn)
+            for _ in range(reps):
+                for m in range(n_mat):
+                    fn(ws[m], x, rows, n, y=ys[m], status=st, tuning=tn)
         ms_pass, n_pass, total = _timed_loop(torch, g.replay, chunk=16)
-        us = ms_pass * 1e3 / n_mat
+        us = ms_pass * 1e3 / (n_mat * reps)
         gbs = bytes_call / us / 1e3
         out[key] = {"us_per_call": round(us, 3), "value": round(gbs, 1), "unit": UNIT, "timed_ms": round(total, 1),
+                    "calls_per_graph": n_mat * reps,
                     "roofline": {"bound": "hbm", "achieved": round(gbs, 1), "peak": peaks["hbm"],
                                  "frac": round(gbs / peaks["hbm"], 4), "peak_source": peaks["hbm_src"]}}
     if int(st.item()) != 0:
@@ -1064,10 +1086,12 @@ def run_allgather_share(args):
                 fn()
             torch.cuda.current_stream().wait_stream(side)
             torch.cuda.synchronize()
+            ppg = max(1, args.passes_per_graph)
             g = torch.cuda.CUDAGraph()
             with torch.cuda.graph(g, capture_error_mode="thread_local"):
-                fn()
-            ms = time_graph(torch, dist, world, dev, g.replay, args.passes_per_step, max(2, min(args.steps, 8)), 1)
+                for _ in range(ppg):
+                    fn()
+            ms = time_graph(torch, dist, world, dev, g.replay, max(1, args.passes_per_step // ppg), max(2, min(args.steps, 8)), 1)
             res[name] = round(ms * 1e3 / (max(2, min(args.steps, 8)) * args.passes_per_step), 3)
             if name == "matvec_launches_only_us":
                 leg.gather.finish(leg.status)     # end the step the replays left open
@@ -1132,6 +1156,8 @@ def main():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=40)
     ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--passes-per-graph", type=int, default=PASSES_PER_GRAPH,
+                    help="passes captured in one CUDA graph (a graph launch starts only after the one before it has completed)")
     ap.add_argument("--passes-per-step", type=int, default=PASSES_PER_STEP,
                     help="16-matrix passes per step (a step is this many graph replays)")
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")

@@ -316,6 +316,7 @@ int axc_cuda_q4k_prefill_form(const void* q, const uint16_t* a_bf16, float* c, u
  * for axc_cuda_q4k_matvec_allgather.  No counterpart in the reference (it has neither a
  * multi-GPU path nor a model); this is the linear layer of the 70B-shaped decode sweep. */
 #define AXC_FINISH_OVERLAP_PREVIOUS 1u
+#define AXC_FINISH_LET_NEXT_START 2u
 typedef struct axc_xsrc {
     const float* x;
     const float* x2;
@@ -351,6 +352,14 @@ int axc_cuda_gather_next_epoch(uint32_t* epoch, void* stream);
  * flags: AXC_FINISH_OVERLAP_PREVIOUS lets the kernel start before the launch directly before it
  * in the stream has completed (it polls for that launch's words anyway); the caller guarantees
  * that launch neither advances the epoch nor reads or writes `out`.
+ * AXC_FINISH_LET_NEXT_START (axc_cuda_gather_finish only) keeps the wait for the launch before it
+ * but lets the launches BEHIND it be scheduled at once, as an independent matvec launch
+ * (tuning.pdl = 3) does: the caller states that those launches, up to the next ordered one, read
+ * neither `out` nor anything else a launch still in flight writes before their own dependency
+ * wait.  The matvec launches of the next step then stream their weights while this launch waits for
+ * the step's words, and a stream (or a CUDA graph) of several steps never drains at the end of a
+ * step; their stores still wait for this launch, and so for the epoch it advances.  Without the
+ * flag the launch is ordered: nothing behind it starts before everything before it is complete.
  * sync (nullable): the end-of-step handshake for callers whose ranks are not kept in step by the
  * data they exchange.  The last CTA of the launch stores the epoch it consumed into entry `rank`
  * of every rank's done array (a peer store), waits (bounded, then bit 4 of *status) until its own

@@ -65,7 +65,7 @@ def _gather_worker(rank, world, port, out_dir):
             for s in range(slots):
                 pg.matvec(q_dev[s], torch.from_numpy(xs[s]).to(dev), n_sb, s, status=st,
                           tuning=ops.make_tuning(pdl=3 if s else 2))
-            pg.finish(st)
+            pg.finish(st, let_next_start=bool(step % 2))
             torch.cuda.synchronize(dev)
             assert int(st.item()) == 0, f"rank {rank} step {step}: status {int(st.item())}"
             for s in range(slots):
@@ -81,6 +81,26 @@ def _gather_worker(rank, world, port, out_dir):
             # matvec (stores into this rank's memory) while this one has not even begun
             if rank == 1:
                 time.sleep(0.05)
+        # Steps back to back with nothing between them: every launch declared independent and the
+        # finish launches letting the next step's matvecs start while they still wait, so steps
+        # overlap on the GPU.  x differs per step; only the last step's vectors are read.
+        burst = 5
+        xs_dev = [[torch.from_numpy(synth.activations(n_sb * 256, 900 + 10 * t + s)).to(dev) for s in range(slots)]
+                  for t in range(burst)]
+        torch.cuda.synchronize(dev)
+        e0 = int(pg.epoch.item())
+        for t in range(burst):
+            for s in range(slots):
+                pg.matvec(q_dev[s], xs_dev[t][s], n_sb, s, status=st, tuning=ops.make_tuning(pdl=3))
+            pg.finish(st, let_next_start=True)
+        torch.cuda.synchronize(dev)
+        assert int(st.item()) == 0, f"rank {rank} burst: status {int(st.item())}"
+        assert int(pg.epoch.item()) == e0 + burst
+        for s in range(slots):
+            x_last = synth.activations(n_sb * 256, 900 + 10 * (burst - 1) + s)
+            y_ref = oracle.matvec_rows("q4k", q_full[s], x_last, rows, n_sb)
+            _y64, mag = oracle.matvec_rows_f64("q4k", q_full[s], x_last, rows, n_sb)
+            assert (np.abs(pg.vector(s).cpu().numpy() - y_ref) / mag).max() <= 1e-5, f"rank {rank} burst slot {s}"
         open(os.path.join(out_dir, f"gather_ok{rank}"), "w").write("ok")
         dist.barrier()
     finally:

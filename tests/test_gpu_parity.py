@@ -231,7 +231,8 @@ def test_q4k_fused_allgather_epilogue_single_rank(synth):
             pg.matvec(dev(q), dev(x), n_sb, slot, status=st,
                       tuning=ops_.make_tuning(pdl=3 if slot else 2))
             cases.append((q, x))
-        pg.finish(st)
+        # on odd iterations the finish launch lets the launches behind it start while it waits
+        pg.finish(st, let_next_start=bool(it % 2))
         for slot, (q, x) in enumerate(cases):
             y = pg.vector(slot)
             y_plain = ops_.q4k_matvec(dev(q), dev(x), rows, n_sb)
