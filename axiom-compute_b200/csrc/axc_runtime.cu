@@ -1009,6 +1009,7 @@ int axc_cuda_q4k_prepare_x(const axc_xsrc* xs, void* image, float* plain_out, ui
         return fail(AXC_ERR_INVALID_ARGUMENT, "only (value, epoch) sources may overlap the launch before");
     axc::XSource src;
     src.x = xs->x, src.x2 = xs->x2, src.x_pairs = xs->x_pairs, src.x2_pairs = xs->x2_pairs, src.epoch_ptr = xs->epoch;
+    src.parity_stride_bytes = xs->parity_stride_bytes;
     return launch_result(axc::launch_q4_prepare_x(src, image, plain_out, n_superblocks * 4u, status, (cudaStream_t)stream,
                                                   (flags & AXC_FINISH_OVERLAP_PREVIOUS) != 0));
 }

@@ -115,7 +115,7 @@ def _decode_worker(rank, world, port, out_dir):
         decode = load_pkg("decode")
         dev = torch.device("cuda", rank)
         shape = decode.SweepShape(hidden=512, kv=128, ffn=1024, layers=3)
-        for mode in ("fused", "paired"):
+        for mode in ("fused", "prepared", "mixed", "poll", "paired"):
             if mode not in decode.MODES:
                 continue
             sweep = decode.DecodeSweep(shape, dev, seed=4242, mode=mode)
