@@ -100,6 +100,7 @@ class ClockSampler:
 
     def __init__(self, index: int):
         self.samples, self.reasons, self.max_mhz, self.ok = [], set(), None, False
+        self.power_w, self.power_limit_w = [], None
         self._stop = threading.Event()
         self._thr = None
         try:
@@ -108,6 +109,10 @@ class ClockSampler:
             pynvml.nvmlInit()
             self.h = pynvml.nvmlDeviceGetHandleByIndex(index)
             self.max_mhz = int(pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM))
+            try:   # read only: the limit in force, for the power figures beside the clocks
+                self.power_limit_w = round(pynvml.nvmlDeviceGetEnforcedPowerLimit(self.h) / 1000.0, 1)
+            except Exception:
+                self.power_limit_w = None
             self.ok = True
         except Exception:
             self.ok = False
@@ -131,6 +136,7 @@ class ClockSampler:
                 for k, bit in names.items():
                     if mask & bit:
                         self.reasons.add(k)
+                self.power_w.append(nv.nvmlDeviceGetPowerUsage(self.h) / 1000.0)
             except Exception:
                 pass
             time.sleep(0.005)
@@ -154,6 +160,10 @@ class ClockSampler:
                "sampled": "inside the timed region only"}
         if elapsed_ms is not None:
             out["ms_times_mhz"] = round(elapsed_ms * med, 1)
+        if self.power_w:
+            out["power_w"] = {"median": round(statistics.median(self.power_w), 1), "max": round(max(self.power_w), 1),
+                              "limit": self.power_limit_w,
+                              "note": "NVML board power: a moving average that lags a sub-second run"}
         return out
 
 
