@@ -32,6 +32,7 @@ from __future__ import annotations
 import argparse
 import importlib
 import json
+import math
 import os
 import statistics
 import struct
@@ -487,9 +488,7 @@ def run_ours(args):
     # all-gather together with programmatic-dependent-launch kernels hung on this stack.
     use_graph = not args.no_graph and (world == 1 or leg.gather is not None or args.force_graph)
     pps = max(1, args.passes_per_step)
-    ppg = max(1, args.passes_per_graph)
-    if pps % ppg:
-        raise SystemExit("--passes-per-step must be a multiple of --passes-per-graph")
+    ppg = math.gcd(pps, max(1, args.passes_per_graph))   # whole graphs per step
     run_pass = leg.graph_for("main", tuning, use_graph, ppg)
     warm = max(args.warmup, 3)
     sampler = ClockSampler(local_rank)
